@@ -55,7 +55,13 @@ struct AttnMmaArgs {
     int n_layers, layer;         // layers in the cache group, this layer's index
     int* status;                 // set non-zero if a bounded wait gives up
     int recv_rows;               // cluster variant: most packed rows any request of the step has (sizes what a block receives)
+    const float* sink;           // [H] or null: a logit per query head that joins the softmax's denominator once (no key, no value)
 };
+
+// What a sink adds to a row's denominator once every key has been seen: exp(sink - m), m the row's final maximum.
+__device__ __forceinline__ float att_sink_term(const float* sink, int head, float m) {
+    return sink != nullptr ? __expf(sink[head] - m) : 0.f;
+}
 
 // Span length (keys) of the keys kernel for a step whose longest request covers `range` keys and that has
 // `items` (request, kv head) pairs.  The kernel runs in waves of ATT_KEYS_SLOTS CTAs and a CTA costs about two
@@ -364,7 +370,7 @@ k_attention_rows(AttnMmaArgs a, int n_seg) {
     for (int half = 0; half < 2; half++) {
         int pr = half ? rb : ra;
         if (pr >= rows_total) continue;
-        float inv = 1.0f / l[half];
+        float inv = 1.0f / (l[half] + att_sink_term(a.sink, kvh * a.G + pr % a.G, m[half]));
         __nv_bfloat16* dst = a.out + ((long long)(tok_base + pr / a.G) * a.H + (kvh * a.G + pr % a.G)) * HD;
 #pragma unroll
         for (int d = 0; d < HD / 8; d++)
@@ -696,7 +702,7 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
                 t.x += v.x * f; t.y += v.y * f; t.z += v.z * f; t.w += v.w * f;
                 ll += ml_s[(w * 16 + r) * 2 + 1] * f;
             }
-            const float inv = 1.0f / ll;
+            const float inv = 1.0f / (ll + att_sink_term(a.sink, kvh * a.G + r % a.G, off));
             __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
             __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
             uint2 packed;
@@ -750,7 +756,7 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
             t.x += v.x * wk; t.y += v.y * wk; t.z += v.z * wk; t.w += v.w * wk;
             ll += ml.y * wk;
         }
-        const float inv = 1.0f / ll;
+        const float inv = 1.0f / (ll + att_sink_term(a.sink, kvh * a.G + r % a.G, off));
         __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
         __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
         uint2 packed;
@@ -1084,7 +1090,7 @@ k_attention_keys_even(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs
                 const int q = tid + j * ATT_THREADS;
                 if (q < owned) {
                     const int r = q / QUADS, d = (q % QUADS) * 4;
-                    const float inv = 1.0f / ll[j];
+                    const float inv = 1.0f / (ll[j] + att_sink_term(a.sink, kvh * a.G + r % a.G, mm[j]));
                     __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
                     __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[j].x * inv, acc[j].y * inv), hi2 = __floats2bfloat162_rn(acc[j].z * inv, acc[j].w * inv);
                     uint2 packed;
@@ -1138,7 +1144,7 @@ k_attention_merge(AttnMmaArgs a) {
         float ll = 0.f;                      // summed in a fixed order: lane-strided, then the warp tree
         for (int s = lane; s < n_spans; s += 32) ll += __ldcg(ml + (s * 16 + r) * 2 + 1) * expf(__ldcg(ml + (s * 16 + r) * 2) - off);
         ll = xr_warp_sum(ll);
-        if (lane == 0) { row_max[r] = off; row_inv[r] = 1.0f / ll; }
+        if (lane == 0) { row_max[r] = off; row_inv[r] = 1.0f / (ll + att_sink_term(a.sink, kvh * a.G + r % a.G, off)); }
     }
     __syncthreads();
     constexpr int QUADS = HD / 4;                       // float4 per row
@@ -1255,7 +1261,7 @@ k_attention_merge_small(AttnMmaArgs a) {
         const float off = mm == -INFINITY ? 0.f : mm;
         float ll = 0.f;
         for (int sp = 0; sp < n_spans; sp++) ll += mls[r][sp].y * __expf(mls[r][sp].x - off);
-        inv = 1.0f / ll;
+        inv = 1.0f / (ll + att_sink_term(a.sink, kvh * a.G + r % a.G, off));
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             int sp = g + k * groups;
@@ -1524,13 +1530,14 @@ XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window, long long item
 // flags: n_flags zeroed words that only this kernel touches (it leaves them zero), or null.
 // uneven: the requests' key ranges differ much in length (a hint for the choice between spans and even shares).
 // row_tiles: the 64-row tiles of the portions with more than 16 packed rows, summed, or 0 if the caller does not know.
+// sink: float32 [H] or null; exp(sink[h]) joins the denominator of every softmax of query head h once.
 XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, const int* seg_start, const int* seg_len,
                                const int* seg_pos0, const int* block_tables, float* part_acc, float* part_ml,
                                long long q_stride, long long page_stride, long long v_offset, int n_seg, int H, int K,
                                int hd, int max_pages, int page_size, int window, float scale, int max_seg_len,
                                int max_kv_len, int splits, int any_short, int any_long, const void* cache_base,
                                long long n_pages, int n_layers, int layer, int* status, int* flags, int n_flags,
-                               int uneven, long long row_tiles, cudaStream_t stream) {
+                               int uneven, long long row_tiles, const float* sink, cudaStream_t stream) {
     if (n_seg < 1 || H < 1 || K < 1 || H % K != 0 || hd < 16 || hd > 128 || hd % 16 != 0 || page_size < 1 || window < 0 ||
         (q_stride % 8) != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache_k & 15) || (page_stride % 8) != 0 || (v_offset % 8) != 0)
         return XR_ERR_ARG;
@@ -1539,7 +1546,7 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
     if (any_short && splits < spans) return XR_ERR_ARG;
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  spans, 0, scale, -1, n_layers, layer, status, 16};
+                  spans, 0, scale, -1, n_layers, layer, status, 16, sink};
     { long long rows = (long long)(max_seg_len < 1 ? 1 : max_seg_len) * a.G; a.recv_rows = rows < 16 ? (int)rows : 16; }
     a.span = att_choose_span(att_range(max_kv_len, window), (long long)n_seg * K);
     const long long room = (long long)splits * n_seg * K;

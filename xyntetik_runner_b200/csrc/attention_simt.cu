@@ -26,6 +26,7 @@ struct AttnArgs {
     long long page_stride, v_offset, q_row_stride;
     int n, H, K, hd, max_pages, page_size, window;
     float scale;
+    const float* sink;           // [H] or null: exp(sink[h]) joins the softmax's denominator once (no key, no value)
 };
 
 #define AS_MAX_HD 256
@@ -87,6 +88,7 @@ k_attention_simt(AttnArgs a) {
         m = m_new;
     }
     T* orow = (T*)a.out + (size_t)t * a.H * a.hd + (size_t)h * a.hd;
+    if (a.sink != nullptr) l += expf(a.sink[h] - m);
     float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < ND; i++) {
@@ -98,11 +100,11 @@ k_attention_simt(AttnArgs a) {
 XR_EXPORT int xr_attention_simt(const void* q, void* out, int dtype, const void* cache_k, const int* positions,
                                 const int* tok_seg, const int* block_tables, long long page_stride,
                                 long long v_offset, long long q_row_stride, int n, int H, int K, int hd,
-                                int max_pages, int page_size, int window, float scale, cudaStream_t stream) {
+                                int max_pages, int page_size, int window, float scale, const float* sink, cudaStream_t stream) {
     if (n < 1 || H < 1 || K < 1 || H % K != 0 || hd < 1 || hd > AS_MAX_HD || page_size < 1 || window < 0)
         return XR_ERR_ARG;
     AttnArgs a{q, out, cache_k, positions, tok_seg, block_tables, page_stride, v_offset, q_row_stride,
-               n, H, K, hd, max_pages, page_size, window, scale};
+               n, H, K, hd, max_pages, page_size, window, scale, sink};
     long long warps = (long long)n * H;
     long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return XR_ERR_ARG;

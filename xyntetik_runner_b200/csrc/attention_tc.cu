@@ -47,6 +47,7 @@ struct AttnTcArgs {
     int H, K, G, max_pages, page_size, page_shift, window, n_layers, layer;
     float scale_log2;            // scale * log2(e)
     int n_seg;
+    const float* sink;           // [H] or null: exp(sink[h]) joins the denominator of every softmax of query head h once
 };
 
 __device__ __forceinline__ uint32_t ta_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -421,6 +422,8 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             asm volatile("bar.sync 1, 256;" ::: "memory");
             l = x[r] + x[128 + r];
             const bool live = pr < rows_total;
+            // a sink has no key and no value: it only enters the sum, at the offset the sum carries
+            if (live && a.sink != nullptr) l += ta_exp2(fmaf(a.sink[kvh * a.G + pr % a.G], 1.4426950408889634f, -m));
             float inv = live ? 1.0f / l : 0.f;
             __nv_bfloat16* dst = a.out + ((long long)(tok_base + (live ? pr : 0) / a.G) * a.H + (kvh * a.G + (live ? pr : 0) % a.G)) * HD + half * (HD / 2);
             float v[32];
@@ -479,7 +482,8 @@ XR_EXPORT int xr_attention_tc_supported(int H, int K, int hd, int page_size) {
 XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, const int* seg_start, const int* seg_len,
                               const int* seg_pos0, const int* block_tables, int* status, long long q_row_stride, int n,
                               int n_seg, int H, int K, int hd, int max_pages, int page_size, int window, float scale,
-                              int max_seg_len, long long row_tiles, long long n_pages, int n_layers, int layer, cudaStream_t stream) {
+                              int max_seg_len, long long row_tiles, long long n_pages, int n_layers, int layer, const float* sink,
+                              cudaStream_t stream) {
     if (!xr_attention_tc_supported(H, K, hd, page_size) || n < 1 || n_seg < 1 || window < 0 || status == nullptr) return XR_ERR_ARG;
     if (((uintptr_t)q & 15) || ((uintptr_t)cache_base & 15) || (q_row_stride % 8) != 0) return XR_ERR_ARG;
     const int G = H / K;
@@ -518,7 +522,7 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     int shift = 0;
     while ((1 << shift) < page_size) shift++;
     AttnTcArgs a{(__nv_bfloat16*)out, seg_start, seg_len, seg_pos0, block_tables, status, H, K, G, max_pages, page_size, shift,
-                 window, n_layers, layer, scale * 1.4426950408889634f, n_seg};
+                 window, n_layers, layer, scale * 1.4426950408889634f, n_seg, sink};
     constexpr int SMEM = 10 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
     if (!configured) {

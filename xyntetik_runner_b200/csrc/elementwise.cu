@@ -357,7 +357,9 @@ XR_EXPORT int xr_rmsnorm_act(const void* in, int dtype, long long ld_in, const f
 //
 // in: [n, ld_in] rows as one projection wrote them: Q heads [H][D], then K heads [K][D], then V heads [K][Vd].
 // Every Q and K head is divided by its root mean square (eps inside the root) and multiplied by a weight of D values
-// that all heads share (q_w, k_w; null: no norm), in float32; then the first rotary_dim elements are rotated, pair
+// that all heads share (q_w, k_w; null: no norm, or with `unit` a norm without a weight), in float32; the Q heads are
+// then multiplied by a factor that grows with the position p, 1 + q_coef ln(floor((p + 1) / q_every) + 1) (q_every 0:
+// no factor); then the first rotary_dim elements are rotated, pair
 // (2j, 2j + 1) or (j, j + rotary_dim/2), by angle = position * freq[j] (a float64 product brought into [-pi, pi] in
 // float64, cosine and sine in float32).  The attention kernels take one head size hd >= max(D, Vd) for keys and
 // values: Q goes to q_out [n, q_ld] (head h at h * hd), K and V to the token's cache rows, each head filled up to hd
@@ -379,6 +381,8 @@ struct QkNormStoreArgs {
     int H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent;
     float eps;
     int pairs;                   // every size, stride and base address is even in elements (set by the launcher)
+    int unit;                    // with null weights: divide by the root mean square all the same
+    float q_coef; int q_every;   // the queries' factor by position (q_every 0: none)
 };
 
 template <typename T>
@@ -400,6 +404,7 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
         kdst = (T*)a.cache_k + (size_t)page * a.page_stride + (size_t)(pos % a.page_size) * a.hd;
     }
     const size_t head_step = (size_t)a.page_size * a.hd;
+    const float q_factor = a.q_every > 0 ? 1.0f + a.q_coef * logf((float)((pos + 1) / a.q_every) + 1.0f) : 1.0f;
     __syncthreads();
     xr_pdl_wait();
     const T* row = (const T*)a.in + (size_t)t * a.ld_in;
@@ -420,17 +425,19 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
             for (int e = lane; e < a.D; e += 32) { const float x = xr_to_f32<T>(src[e]); mine[e] = x; ss = fmaf(x, x, ss); }
         }
         ss = xr_warp_sum(ss);
-        const float inv = w != nullptr ? 1.0f / sqrtf(ss / (float)a.D + a.eps) : 1.0f;
+        const bool normed = w != nullptr || a.unit;
+        float inv = normed ? 1.0f / sqrtf(ss / (float)a.D + a.eps) : 1.0f;
+        if (head < a.H) inv *= q_factor;
         __syncwarp();
         T* dst = head < a.H ? (T*)a.q_out + (size_t)t * a.q_ld + (size_t)head * a.hd : kdst + (size_t)(head - a.H) * head_step;
         auto value = [&](int e) -> float {
             if (e >= a.D) return 0.f;
-            float y = w != nullptr ? mine[e] * inv * w[e] : mine[e];
+            float y = w != nullptr ? mine[e] * inv * w[e] : mine[e] * inv;
             if (e < a.rotary_dim) {
                 int j, other; bool first;
                 if (a.adjacent) { j = e >> 1; first = !(e & 1); other = e ^ 1; }
                 else { first = e < half; j = first ? e : e - half; other = first ? e + half : e - half; }
-                const float z = w != nullptr ? mine[other] * inv * w[other] : mine[other];
+                const float z = w != nullptr ? mine[other] * inv * w[other] : mine[other] * inv;
                 y = first ? y * cs[j] - z * cs[half + j] : y * cs[j] + z * cs[half + j];
             }
             return y;
@@ -466,13 +473,16 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
 XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, void* q_out, long long q_ld, const int* positions,
                                     const int* tok_seg, const int* block_tables, const double* freq, const float* q_w, const float* k_w,
                                     void* cache_k, long long page_stride, long long v_offset, int n, int H, int K, int D, int Vd, int hd,
-                                    int rotary_dim, int max_pages, int page_size, int adjacent_pairs, float eps, cudaStream_t stream) {
+                                    int rotary_dim, int max_pages, int page_size, int adjacent_pairs, float eps, int unit_norm,
+                                    float q_coef, int q_every, cudaStream_t stream) {
     if (n < 1 || H < 1 || K < 1 || D < 1 || Vd < 1 || hd < D || hd < Vd || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) ||
-        page_size < 1 || (rotary_dim > 0 && freq == nullptr) || (q_w == nullptr) != (k_w == nullptr))
+        page_size < 1 || (rotary_dim > 0 && freq == nullptr) || (q_w == nullptr) != (k_w == nullptr) || q_every < 0 ||
+        (unit_norm && q_w != nullptr))
         return XR_ERR_ARG;
     const int pairs = !((D | hd | ld_in | q_ld | page_stride) & 1) && !(((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)cache_k) & 3);
     QkNormStoreArgs a{in, ld_in, q_out, q_ld, positions, tok_seg, block_tables, freq, q_w, k_w, cache_k, page_stride, v_offset,
-                      H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps, pairs};
+                      H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps, pairs, unit_norm ? 1 : 0,
+                      q_coef, q_every};
     const size_t smem = ((size_t)rotary_dim + 8 * (size_t)D) * sizeof(float);
     if (smem > 48 * 1024) return XR_ERR_ARG;
     if (dtype == XR_F32) xr_launch((k_qk_norm_rope_store<float>), dim3(n), dim3(256), smem, stream, a);
@@ -567,6 +577,79 @@ XR_EXPORT int xr_scaled_add(float* x, const float* d, float m, int n, int width,
     size_t total = (size_t)n * width;
     int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
     xr_launch(k_scaled_add, dim3(blocks), dim3(256), 0, stream, x, d, m, total);
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// x[t][i] += x0[t][i] + v[i] on float32 streams (x0 null: the vector alone): the start of a pass of a model that runs a
+// span of layers several times, where the embedding's output and a vector of the pass join the stream.
+// ---------------------------------------------------------------------------
+__global__ void k_stream_step(float* __restrict__ x, const float* __restrict__ x0, const float* __restrict__ v, int width, size_t total) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float add = v != nullptr ? v[i % (size_t)width] : 0.f;
+        if (x0 != nullptr) add += x0[i];
+        x[i] += add;
+    }
+}
+
+XR_EXPORT int xr_stream_step(float* x, const float* x0, const float* v, int n, int width, cudaStream_t stream) {
+    if (n < 1 || width < 1 || (x0 == nullptr && v == nullptr)) return XR_ERR_ARG;
+    size_t total = (size_t)n * width;
+    int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
+    xr_launch(k_stream_step, dim3(blocks), dim3(256), 0, stream, x, x0, v, width, total);
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// An output gate on attention heads: o[t][h][d] *= sigmoid(g[t][h * Vd + d]) (a gate per element, `each`) or
+// sigmoid(g[t][h]) (a gate per head), for d < Vd of every head's hd columns; the sigmoid and the product in float32.
+// g are columns of the projection's rows (row stride ld_g).  Two elements a thread where the sizes are even.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void k_sigmoid_gate(T* __restrict__ o, long long ld_o, const T* __restrict__ g, long long ld_g, int H, int hd, int Vd, int each, int two) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int t = blockIdx.x;
+    T* orow = o + (size_t)t * ld_o;
+    const T* grow = g + (size_t)t * ld_g;
+    if (sizeof(T) == 2 && two) {
+        const int half_v = Vd >> 1, per = H * half_v;
+        for (int i = threadIdx.x; i < per; i += blockDim.x) {
+            const int h = i / half_v, d = (i % half_v) * 2;
+            __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(orow) + (size_t)h * hd + d);
+            const float2 x = __bfloat1622float2(*dst);
+            float ga, gb;
+            if (each) {
+                const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(grow) + (size_t)h * Vd + d));
+                ga = gg.x; gb = gg.y;
+            } else {
+                ga = gb = xr_to_f32<T>(grow[h]);
+            }
+            *dst = __floats2bfloat162_rn(x.x / (1.0f + expf(-ga)), x.y / (1.0f + expf(-gb)));
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < H * Vd; i += blockDim.x) {
+        const int h = i / Vd, d = i % Vd;
+        const float gv = xr_to_f32<T>(grow[each ? i : h]);
+        T* dst = orow + (size_t)h * hd + d;
+        *dst = xr_from_f32<T>(xr_to_f32<T>(*dst) / (1.0f + expf(-gv)));
+    }
+}
+
+XR_EXPORT int xr_sigmoid_gate(void* o, long long ld_o, const void* g, long long ld_g, int dtype, int n, int H, int hd, int Vd, int each,
+                              cudaStream_t stream) {
+    if (n < 1 || H < 1 || Vd < 1 || hd < Vd) return XR_ERR_ARG;
+    const int two = !((hd | Vd | ld_o | ld_g) & 1) && !(((uintptr_t)o | (uintptr_t)g) & 3);
+    const int work = H * Vd / (dtype == XR_BF16 && two ? 2 : 1);
+    const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == XR_F32) xr_launch((k_sigmoid_gate<float>), dim3(n), dim3(threads), 0, stream, (float*)o, ld_o, (const float*)g, ld_g, H, hd, Vd, each ? 1 : 0, 0);
+    else if (dtype == XR_BF16)
+        xr_launch((k_sigmoid_gate<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, (__nv_bfloat16*)o, ld_o, (const __nv_bfloat16*)g, ld_g, H, hd, Vd,
+                  each ? 1 : 0, two);
+    else return XR_ERR_ARG;
     return xr_launch_status();
 }
 

@@ -53,23 +53,25 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_act_mul": [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
-        "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
         "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
         "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
-                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _ll, _vp],
+                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _ll, _vp, _vp],
         "xr_attention_mma_splits": [_i, _i, _ll],
         "xr_attention_even_launches": [],
         "xr_attention_wait_probe": [_vp, _vp, ctypes.c_uint, _vp],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
-        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp],
+        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
         "xr_random_normal": [_vp, _i, _ll, ctypes.c_ulonglong, ctypes.c_ulonglong, _f, _f, _vp],
         "xr_scaled_add": [_vp, _vp, _f, _i, _i, _vp],
+        "xr_stream_step": [_vp, _vp, _vp, _i, _i, _vp],
+        "xr_sigmoid_gate": [_vp, _ll, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp],
         "xr_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_softcap": [_vp, _f, _ll, _vp],
         "xr_latent_prep": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
@@ -79,7 +81,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_latent_attention_mma": [_vp, _ll, _ll, _vp, _ll, _i, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
         "xr_heads_gather": [_vp, _ll, _i, _vp, _i, _i, _i, _i, _vp],
         "xr_heads_scatter_gate": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
-        "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
         "xr_rmsnorm_act": [_vp, _i, _ll, _vp, _vp, _ll, _i, _i, _f, _vp],
         "xr_delta": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
         "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _vp],
@@ -204,11 +206,13 @@ def rmsnorm_act(inp: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: floa
 def qk_norm_rope_store(inp: torch.Tensor, q_out: torch.Tensor, positions, tok_seg, block_tables, freq: Optional[torch.Tensor],
                        q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], cache_k_ptr: Optional[int], page_stride: int, v_offset: int,
                        H: int, K: int, D: int, Vd: int, hd: int, rotary_dim: int, max_pages: int, page_size: int, adjacent: bool,
-                       eps: float) -> None:
+                       eps: float, unit_norm: bool = False, q_coef: float = 0.0, q_every: int = 0) -> None:
     """inp [n, >= (H + K) D + K Vd] (rows may be strided): Q heads, K heads (D each), V heads (Vd each).  Every Q and K head is
     RMS-normed with the weight q_w / k_w (float32 [D], shared by the heads; None: no norm), its first `rotary_dim` elements rotated
     (freq: float64 [rotary_dim / 2]); Q goes to q_out [n, *] (head h at column h * hd), K and V into the token's cache rows, every
-    head filled up to `hd` elements with zeros (cache_k_ptr None: nothing is stored)."""
+    head filled up to `hd` elements with zeros (cache_k_ptr None: nothing is stored).  `unit_norm` (with no weights): every Q
+    and K head is divided by its root mean square all the same.  `q_every` > 0: the Q heads of the token at position p are
+    multiplied by 1 + q_coef ln(floor((p + 1) / q_every) + 1)."""
     _dev(positions, tok_seg, block_tables, freq, q_w, k_w)
     n = inp.shape[0]
     assert inp.stride(1) == 1 and q_out.stride(1) == 1 and inp.dtype == q_out.dtype and q_out.shape[0] == n and q_out.shape[1] >= H * hd
@@ -217,7 +221,8 @@ def qk_norm_rope_store(inp: torch.Tensor, q_out: torch.Tensor, positions, tok_se
     _check(lib().xr_qk_norm_rope_store(inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), q_out.data_ptr(), q_out.stride(0),
                                        positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), _ptr(q_w), _ptr(k_w),
                                        cache_k_ptr, page_stride, v_offset, n, H, K, D, Vd, hd, rotary_dim, max_pages, page_size,
-                                       int(adjacent), float(eps), _stream()), "qk_norm_rope_store")
+                                       int(adjacent), float(eps), int(unit_norm), float(q_coef), int(q_every), _stream()),
+           "qk_norm_rope_store")
     _count()
 
 
@@ -262,15 +267,17 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
 
 def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, positions, tok_seg,
                    block_tables, page_stride: int, v_offset: int, H: int, K: int, hd: int, max_pages: int,
-                   page_size: int, window: int, scale: float) -> None:
-    """Causal attention of every token of the step over its request's pages, float32 arithmetic."""
-    _dev(out, positions, tok_seg, block_tables)
+                   page_size: int, window: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of every token of the step over its request's pages, float32 arithmetic.  `sink`: float32 [H];
+    exp(sink[h]) joins the denominator of head h's softmax once (it has no key and no value)."""
+    _dev(out, positions, tok_seg, block_tables, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
     n = out.shape[0]
     assert out.shape[1] == H * hd and q.dtype == out.dtype
     _check(lib().xr_attention_simt(q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache_k_ptr,
                                    positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), page_stride,
                                    v_offset, q_row_stride, n, H, K, hd, max_pages, page_size, window, float(scale),
-                                   _stream()), "attention_simt")
+                                   _ptr(sink), _stream()), "attention_simt")
     _count()
 
 
@@ -594,7 +601,8 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                   block_tables, part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], page_stride: int,
                   v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
                   n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool,
-                  group: Optional[tuple] = None, uneven: bool = False, row_tiles: int = 0) -> None:
+                  group: Optional[tuple] = None, uneven: bool = False, row_tiles: int = 0,
+                  sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
     (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
     and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel.
@@ -602,8 +610,10 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
     key-split kernel fetch whole page blocks with bulk copies (head sizes 64 and 128, power-of-two pages).
     `uneven`: the requests' lengths differ much; the kernel then cuts the tiles of all requests into even shares from
     fewer requests on than it does otherwise.  row_tiles: ``long_row_tiles(lengths, H // K, 64)``, which sizes the
-    row-tiled kernel's grid exactly; 0: every portion gets the blocks of the longest."""
-    _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml)
+    row-tiled kernel's grid exactly; 0: every portion gets the blocks of the longest.  `sink`: float32 [H]; exp(sink[h])
+    joins the denominator of head h's softmax once."""
+    _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[1] == H * hd
     if any_short:
         assert part_acc is not None and part_acc.numel() >= n_seg * K * splits * 16 * hd
@@ -616,7 +626,7 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                                   group[0] if group else None, group[1] if group else 0, group[2] if group else 1,
                                   group[3] if group else 0, ws.status.data_ptr() if group else None,
                                   ws.flags.data_ptr() if group else None, ws.flags.numel() if group else 0, int(uneven),
-                                  row_tiles, _stream()), "attention_mma")
+                                  row_tiles, _ptr(sink), _stream()), "attention_mma")
     _count((1 if any_long else 0) + (2 if any_short else 0))
 
 
@@ -626,19 +636,20 @@ def attention_tc_supported(dtype: torch.dtype, H: int, K: int, hd: int, page_siz
 
 def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_pos0, block_tables, group: tuple,
                  H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float, n_seg: int,
-                 max_seg_len: int, row_tiles: int = 0) -> None:
+                 max_seg_len: int, row_tiles: int = 0, sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of the portions with more than 16 packed rows on tcgen05 (S and O in tensor memory).
     qkv: the step's fused rows (Q heads first); group = (pointer to the cache group's array, pages, layers, layer).
     row_tiles: ``long_row_tiles(lengths, H // K, 128)``, which sizes the grid exactly; 0: every portion gets the blocks
-    of the longest."""
-    _dev(qkv, out, seg_start, seg_len, seg_pos0, block_tables)
+    of the longest.  `sink`: float32 [H]; exp(sink[h]) joins the denominator of head h's softmax once."""
+    _dev(qkv, out, seg_start, seg_len, seg_pos0, block_tables, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
     n = qkv.shape[0]
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (n, H * hd)
     status = tc_workspace(out.device)[1]
     _check(lib().xr_attention_tc(qkv.data_ptr(), out.data_ptr(), group[0], seg_start.data_ptr(), seg_len.data_ptr(),
                                  seg_pos0.data_ptr(), block_tables.data_ptr(), status.data_ptr(), qkv.stride(0), n, n_seg,
                                  H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, row_tiles, group[1], group[2],
-                                 group[3], _stream()), "attention_tc")
+                                 group[3], _ptr(sink), _stream()), "attention_tc")
     _count()
 
 
@@ -649,6 +660,26 @@ def scaled_add(x: torch.Tensor, d: torch.Tensor, m: float) -> None:
     _dev(x, d)
     assert x.dtype == torch.float32 and d.dtype == torch.float32 and x.shape == d.shape
     _check(lib().xr_scaled_add(x.data_ptr(), d.data_ptr(), float(m), x.shape[0], x.shape[1], _stream()), "scaled_add")
+    _count()
+
+
+def stream_step(x: torch.Tensor, x0: Optional[torch.Tensor], v: Optional[torch.Tensor]) -> None:
+    """x[t] += x0[t] + v on float32 streams [n, width]; v a float32 vector of width values; either may be None."""
+    _dev(x, x0, v)
+    assert x.dtype == torch.float32 and x.is_contiguous() and (x0 is None or (x0.dtype == torch.float32 and x0.shape == x.shape and x0.is_contiguous()))
+    assert v is None or (v.dtype == torch.float32 and v.numel() == x.shape[1] and v.is_contiguous())
+    _check(lib().xr_stream_step(x.data_ptr(), _ptr(x0), _ptr(v), x.shape[0], x.shape[1], _stream()), "stream_step")
+    _count()
+
+
+def sigmoid_gate(o: torch.Tensor, g: torch.Tensor, H: int, hd: int, Vd: int, each: bool) -> None:
+    """o [n, H * hd] (hd columns a head, of which the first Vd are the head's) times sigmoid(g), in place: g [n, H * Vd], a gate
+    per element (`each`), or g [n, H], a gate per head.  Rows of g may be strided (columns of a wider product)."""
+    _dev(o)
+    n = o.shape[0]
+    assert g.is_cuda and o.dtype == g.dtype and o.stride(1) == 1 and g.stride(1) == 1 and o.shape[1] == H * hd and g.shape == (n, H * Vd if each else H)
+    _check(lib().xr_sigmoid_gate(o.data_ptr(), o.stride(0), g.data_ptr(), g.stride(0), dtype_code(o.dtype), n, H, hd, Vd, int(each),
+                                 _stream()), "sigmoid_gate")
     _count()
 
 

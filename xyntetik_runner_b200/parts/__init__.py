@@ -12,4 +12,4 @@ from .mlstm import MLSTM
 from .moe import RoutedExperts
 from .norm import RMSNorm
 from .position import NoPosition, Rope
-from .stream import StreamJoin
+from .stream import StreamJoin, StreamStep

@@ -14,6 +14,14 @@ another size than the query/key heads.  With either, the projection's rows go th
 (angles from float64 products) and stores; keys and values are then cached with one head size, the larger of the two
 rounded up to a multiple of 16 and filled with zeros, which changes no score and no sum, and the output product's
 matrix gets zero columns to match.
+
+Further options, all on that general path.  `qk_norm="unit"`: every query and key head is divided by its root mean square,
+without a weight.  `q_temp=(c, n)`: the queries at position p are multiplied by 1 + c ln(floor((p + 1) / n) + 1), a factor
+that grows by steps with the position.  `sink`: a learned logit per query head that joins the softmax's denominator once
+and has no key and no value (every attention kernel adds exp(sink - m) to a row's sum when the row is complete).  `gate`:
+the heads' outputs are multiplied by sigmoid(W_g h) before the output product, "each" element by its own gate (W_g of
+H x Vd rows) or "head" by head (W_g of H rows); W_g's rows ride in the fused projection.  Biases (`bias`, with
+`bias_suffix`; `out_bias` for the output product's) combine with all of these.
 """
 from __future__ import annotations
 
@@ -44,16 +52,21 @@ class GQAAttention(Mixer):
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, position: PositionEncoding,
                  prefix: str, bias: bool = False, window: Optional[int] = None, scale: Optional[float] = None,
                  q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj", weight_suffix: str = ".weight",
-                 value_dim: Optional[int] = None, qk_norm: bool = False, norm_eps: float = 1e-6,
-                 q_norm: str = "q.norm", k_norm: str = "k.norm"):
+                 value_dim: Optional[int] = None, qk_norm=False, norm_eps: float = 1e-6,
+                 q_norm: str = "q.norm", k_norm: str = "k.norm", bias_suffix: str = ".bias", out_bias: Optional[bool] = None,
+                 q_temp: Optional[tuple] = None, sink: Optional[str] = None, gate: Optional[str] = None, g: str = "g"):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
+        if qk_norm not in (False, True, "unit"):
+            raise ValueError(f"{prefix}: qk_norm is False, True (a weight per element) or 'unit' (no weight)")
+        if gate not in (None, "head", "each"):
+            raise ValueError(f"{prefix}: gate is None, 'head' or 'each'")
+        if q_temp is not None and (len(q_temp) != 2 or int(q_temp[1]) < 1):
+            raise ValueError(f"{prefix}: q_temp is (coefficient, positions per step >= 1)")
         self.D = head_dim                                      # query/key elements per head
         self.Vd = head_dim if value_dim is None else value_dim  # value elements per head
         # the general path: a norm per head, or values of another size than keys
-        self.general = bool(qk_norm) or self.Vd != self.D
-        if self.general and bias:
-            raise ValueError(f"{prefix}: biases are not combined with qk_norm or value_dim")
+        self.general = bool(qk_norm) or self.Vd != self.D or q_temp is not None or gate is not None
         # head size of the cache and of the attention kernels
         hd = -(-max(self.D, self.Vd) // 16) * 16 if self.general else head_dim
         if not (1 <= hd <= 256):
@@ -63,8 +76,14 @@ class GQAAttention(Mixer):
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)   # src/model.h:464-467
         self.proj = (q, k, v, o)
         self.suffix = weight_suffix
-        self.qk_norm, self.norm_eps = bool(qk_norm), float(norm_eps)
+        self.qk_norm, self.unit_norm, self.norm_eps = qk_norm is True, qk_norm == "unit", float(norm_eps)
         self.norm_names = (prefix + q_norm, prefix + k_norm)
+        self.bias_suffix, self.out_bias = bias_suffix, bool(bias) if out_bias is None else bool(out_bias)
+        self.q_temp = None if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+        self.sink_name = None if sink is None else prefix + sink
+        self.gate, self.gate_name = gate, prefix + g
+        self.gate_cols = 0 if gate is None else (heads * self.Vd if gate == "each" else heads)
+        self.sink = None
         self.qkv = self.out = None
         self.rot = None
         self.q_norm_w = self.k_norm_w = self.freq64 = None
@@ -78,23 +97,37 @@ class GQAAttention(Mixer):
         qd, kd, vd = self.H * self.D, self.K * self.D, self.K * self.Vd
         t = {q + sfx: TensorSpec((qd, self.width)), k + sfx: TensorSpec((kd, self.width)),
              v + sfx: TensorSpec((vd, self.width)), o + sfx: TensorSpec((self.width, self.H * self.Vd))}
+        b = self.bias_suffix
         if self.bias:
-            t.update({q + ".bias": TensorSpec((qd,), "vector", "zeros"), k + ".bias": TensorSpec((kd,), "vector", "zeros"),
-                      v + ".bias": TensorSpec((kd,), "vector", "zeros"), o + ".bias": TensorSpec((self.width,), "vector", "zeros")})
+            t.update({q + b: TensorSpec((qd,), "vector", "zeros"), k + b: TensorSpec((kd,), "vector", "zeros"),
+                      v + b: TensorSpec((vd,), "vector", "zeros")})
+        if self.out_bias:
+            t[o + b] = TensorSpec((self.width,), "vector", "zeros")
         if self.qk_norm:
             t.update({n: TensorSpec((self.D,), "vector", "ones_jitter") for n in self.norm_names})
+        if self.gate is not None:
+            t[self.gate_name + sfx] = TensorSpec((self.gate_cols, self.width))
+        if self.sink_name is not None:
+            t[self.sink_name] = TensorSpec((self.H,), "vector")
         return t
 
     def bind(self, tensors, rt):
         q, k, v, o = (self.prefix + n for n in self.proj)
         sfx = self.suffix
-        ws = [tensors.pop(n + sfx) for n in (q, k, v)]
+        # the gate's rows ride in the same product, behind Q, K and V
+        fused = (q, k, v) + ((self.gate_name,) if self.gate is not None else ())
+        ws = [tensors.pop(n + sfx) for n in fused]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.to(torch.float32) for w in ws]
         bias = obias = None
         if self.bias:
-            bias = torch.cat([tensors[n + ".bias"].to(torch.float32) for n in (q, k, v)])
-            obias = tensors[o + ".bias"]
+            bias = torch.cat([tensors[n + self.bias_suffix].to(torch.float32) for n in (q, k, v)])
+            if self.gate is not None:
+                bias = torch.cat([bias, torch.zeros(self.gate_cols, dtype=torch.float32, device=bias.device)])
+        if self.out_bias:
+            obias = tensors[o + self.bias_suffix]
+        if self.sink_name is not None:
+            self.sink = tensors[self.sink_name].to(torch.float32).contiguous()
         self.qkv = Linear(torch.cat(ws, dim=0), bias).prepare(rt)
         del ws
         wo = tensors[o + sfx]
@@ -147,12 +180,15 @@ class GQAAttention(Mixer):
         rot_dim, rot_freq, adjacent, mscale = self.rot
         if self.general:
             # the projection's rows [Q | K | V] in their own sizes; norm, rotation and store in one kernel, Q into `qkv`
-            cols = (self.H + self.K) * self.D + self.K * self.Vd
+            # (and the gate's columns behind them, which the gate kernel reads after the attention)
+            gate_at = (self.H + self.K) * self.D + self.K * self.Vd
+            cols = gate_at + self.gate_cols
             proj = ctx.buf("attn_proj", (n, -(-cols // 8) * 8), ctx.act_dtype)[:, :cols]
             self.qkv.forward(h, proj)
+            coef, every = self.q_temp if self.q_temp is not None else (0.0, 0)
             kernels.qk_norm_rope_store(proj, qkv, ctx.positions, ctx.tok_seg, bt, self.freq64, self.q_norm_w, self.k_norm_w, store_ptr,
                                        page_stride, v_offset, self.H, self.K, self.D, self.Vd, self.hd, rot_dim, ctx.max_pages,
-                                       ctx.page_size, adjacent, self.norm_eps)
+                                       ctx.page_size, adjacent, self.norm_eps, self.unit_norm, coef, every)
         else:
             pend = self.qkv.forward(h, qkv, defer=True)
             if pend is not None and lay.writes_cache:
@@ -182,7 +218,7 @@ class GQAAttention(Mixer):
                 # prompt portions: S = Q K^T and O += P V on tcgen05
                 kernels.attention_tc(qkv, o, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, ctx.cache_group(lay), self.H,
                                      self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, ctx.n_seg,
-                                     longest, row_tiles=tiles_tc)
+                                     longest, row_tiles=tiles_tc, sink=self.sink)
                 counters["tcgen05"] += 1
                 any_long = False
             if any_short or any_long:
@@ -190,12 +226,14 @@ class GQAAttention(Mixer):
                                       page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
                                       self.window or 0, self.scale, ctx.n_seg, longest, ctx.max_kv_len, splits,
                                       any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None, uneven=ctx.uneven,
-                                      row_tiles=tiles_rows)
+                                      row_tiles=tiles_rows, sink=self.sink)
                 counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
-                                   self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale)
+                                   self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, sink=self.sink)
             counters["simt"] += 1
+        if self.gate is not None:
+            kernels.sigmoid_gate(o, proj[:, gate_at:gate_at + self.gate_cols], self.H, self.hd, self.Vd, self.gate == "each")
         ctx.set_pending(x, self.out.forward(o, x, accumulate=True, defer=True))
 
 

@@ -50,14 +50,22 @@ register_block("prenorm", PreNormBlock)
 
 
 class ParallelBlock(Block):
-    """One norm, and mixer and feed-forward side by side on its output:  h = norm(x);  x += m (mixer(h) + ff(h)).
-    The sublayers add into a float32 stream of their own, which is added to x once, times the multiplier m."""
+    """Mixer and feed-forward side by side, both reading the same x:  x += m (mixer(norm(x)) + ff(norm'(x))), norm' the
+    same norm, or with `ff_norm` a second one with a weight of its own.  With a multiplier m other than one the sublayers
+    add into a float32 stream of their own, which is added to x once, times m.  `direct` (m = 1 only): the norms are taken
+    first and the sublayers' last products add into x themselves, one after the other, with no stream in between."""
 
-    def __init__(self, norm: Norm, mixer: Mixer, feed_forward, residual_mult: float = 1.0):
-        self.norm, self.mixer, self.feed_forward, self.mult = norm, mixer, feed_forward, float(residual_mult)
+    def __init__(self, norm: Norm, mixer: Mixer, feed_forward, residual_mult: float = 1.0, ff_norm: Norm = None,
+                 direct: bool = False):
+        if ff_norm is not None and feed_forward is None:
+            raise ValueError("a second norm comes with a feed-forward")
+        if direct and float(residual_mult) != 1.0:
+            raise ValueError("sublayers add into x directly only with a residual multiplier of one")
+        self.norm, self.mixer, self.feed_forward, self.mult, self.ff_norm = norm, mixer, feed_forward, float(residual_mult), ff_norm
+        self.direct = bool(direct)
 
     def parts(self):
-        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+        return tuple(p for p in (self.norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None)
 
     @property
     def graph_safe(self):
@@ -81,11 +89,21 @@ class ParallelBlock(Block):
         n, width = x.shape
         h = ctx.buf("block_normed", (n, width), ctx.act_dtype)
         self.norm.forward(ctx, x, h)
+        h2 = h
+        if self.ff_norm is not None:
+            # the second norm reads the x the first one read, before any sublayer adds to it
+            h2 = ctx.buf("block_normed_ff", (n, width), ctx.act_dtype)
+            self.ff_norm.forward(ctx, x, h2)
+        if self.direct:
+            self.mixer.forward(ctx, h, x, lay)
+            if self.feed_forward is not None:
+                self.feed_forward.forward(ctx, h2, x)
+            return
         d = ctx.buf("block_sum", (n, width), torch.float32)
         d.zero_()
         self.mixer.forward(ctx, h, d, lay)
         if self.feed_forward is not None:
-            self.feed_forward.forward(ctx, h, d)
+            self.feed_forward.forward(ctx, h2, d)
         ctx.materialize(d)
         kernels.scaled_add(x, d, self.mult)
 

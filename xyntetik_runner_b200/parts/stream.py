@@ -3,6 +3,9 @@
 ``StreamJoin``: x <- W [x; x0], one product over the stream and the embedding's output side by side (W is
 [width, 2 width], the stream's columns first).  A model that runs a span of layers several times with the same
 weights feeds the embedding back in this way at the start of every pass.
+
+``StreamStep``: x <- x (+ x0) + v, v one row of a table [passes, width]: such a model may instead add the embedding's
+output (from the second pass on) and a vector of the pass, in float32.
 """
 from __future__ import annotations
 
@@ -35,3 +38,30 @@ class StreamJoin(Part):
         both = ctx.buf("stream_join", (x.shape[0], 2 * self.width), ctx.act_dtype)
         kernels.concat_cast(x, x0, both)
         self.linear.forward(both, x)
+
+
+class StreamStep(Part):
+    """x += x0 + table[row] (`add_embedding`), or x += table[row] alone; `name` None: no table, the embedding alone."""
+    graph_safe = True
+
+    def __init__(self, width: int, name: str, rows: int, row: int, add_embedding: bool):
+        if name is None and not add_embedding:
+            raise ValueError("a stream step adds the embedding's output, a row of a table, or both")
+        if name is not None and not (0 <= row < rows):
+            raise ValueError(f"row {row} of a table of {rows}")
+        self.width, self.name, self.rows, self.row, self.add_embedding = width, name, rows, row, bool(add_embedding)
+        self.vector = None
+
+    def tensors(self):
+        return {} if self.name is None else {self.name: TensorSpec((self.rows, self.width), kind="vector", init="zeros_jitter")}
+
+    def bind(self, tensors, rt):
+        if self.name is not None:
+            self.vector = tensors[self.name][self.row].to(torch.float32).contiguous()
+
+    def weight_bytes(self):
+        return 0 if self.name is None else self.width * 4
+
+    def forward(self, ctx, x: torch.Tensor, x0: torch.Tensor) -> None:
+        ctx.materialize(x)
+        kernels.stream_step(x, x0 if self.add_embedding else None, self.vector)
