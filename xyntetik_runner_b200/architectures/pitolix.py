@@ -15,9 +15,24 @@ from ..config.pitolix import NAME, PitolixConfig, RotaryAttentionConfig, SinkAtt
 from ..config.registry import register_architecture
 from ..engine.model import ModelPlan, ScheduleEntry
 from ..parts import (Embedding, GatedFeedForward, GQAAttention, Head, NoPosition, ParallelBlock, RMSNorm, Rope, StreamStep)
+from ..weights.loader import TensorSpec
 
 # no position table limits a request's length: the rotation and the query factor take any position
 MAX_POSITIONS = 1 << 30
+
+
+class _Block(ParallelBlock):
+    """A layer without a feed-forward lets a checkpoint carry a second norm weight that nothing reads."""
+
+    def __init__(self, *parts, spare: str = None, **options):
+        super().__init__(*parts, **options)
+        self.spare = spare
+
+    def tensors(self):
+        out = super().tensors()
+        if self.spare is not None:
+            out[self.spare] = TensorSpec((self.norm.width,), kind="vector", init="zeros", optional=True)
+        return out
 
 
 def build_pitolix(cfg: PitolixConfig) -> ModelPlan:
@@ -41,7 +56,8 @@ def build_pitolix(cfg: PitolixConfig) -> ModelPlan:
         if lay.mlp is not None:
             ff = GatedFeedForward(W, lay.mlp.ff, p + "mlp.", "silu", gate="gate", up="up", down="down")
             ff_norm = RMSNorm(W, eps, p + "norm2", one_plus=True)
-        blocks.append(ParallelBlock(RMSNorm(W, eps, p + "norm1", one_plus=True), mixer, ff, ff_norm=ff_norm, direct=True))
+        blocks.append(_Block(RMSNorm(W, eps, p + "norm1", one_plus=True), mixer, ff, ff_norm=ff_norm, direct=True,
+                             spare=None if ff is not None else p + "norm2"))
     # one stream part per pass of the loop: the embedding's output from the second pass on, and the pass's vector
     stream_parts = []
     if cfg.loop is not None:
