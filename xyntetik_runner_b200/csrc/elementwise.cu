@@ -61,7 +61,7 @@ XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, const
 // ---------------------------------------------------------------------------
 template <typename TO>
 __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
-                          TO* __restrict__ out, int d, float eps) {
+                          TO* __restrict__ out, const float* __restrict__ w2, TO* __restrict__ out2, int d, float eps) {
     xr_pdl_launch();
     xr_pdl_wait();
     __shared__ float scratch[33];
@@ -83,7 +83,10 @@ __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ r
 #pragma unroll
         for (int k = 0; k < PER; k++) {
             int i = threadIdx.x + k * blockDim.x;
-            if (i < d) o[i] = xr_from_f32<TO>(v[k] * scale * w[i]);
+            if (i < d) {
+                o[i] = xr_from_f32<TO>(v[k] * scale * w[i]);
+                if (w2) out2[(size_t)blockIdx.x * d + i] = xr_from_f32<TO>(v[k] * scale * w2[i]);
+            }
         }
         return;
     }
@@ -91,7 +94,10 @@ __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ r
     for (int i = threadIdx.x; i < d; i += blockDim.x) { float v = xr[i]; ss += v * v; }
     ss = xr_block_sum(ss, scratch);
     float scale = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
+        if (w2) out2[(size_t)blockIdx.x * d + i] = xr_from_f32<TO>(xr[i] * scale * w2[i]);
+    }
 }
 
 // Rows whose width is a multiple of four: a thread keeps up to eight float4 of the row, so a row needs few
@@ -106,7 +112,7 @@ __device__ __forceinline__ void rms_store4(__nv_bfloat16* o, float4 v) {
 }
 template <typename TO>
 __global__ void k_rmsnorm_vec(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
-                              TO* __restrict__ out, int d, float eps) {
+                              TO* __restrict__ out, const float* __restrict__ w2, TO* __restrict__ out2, int d, float eps) {
     xr_pdl_launch();
     xr_pdl_wait();
     __shared__ float scratch[33];
@@ -133,23 +139,29 @@ __global__ void k_rmsnorm_vec(const float* __restrict__ x, const int* __restrict
         if (i < quads) {
             float4 g = w4[i];
             rms_store4(o + 4 * (size_t)i, make_float4(v[k].x * scale * g.x, v[k].y * scale * g.y, v[k].z * scale * g.z, v[k].w * scale * g.w));
+            if (w2) {
+                g = reinterpret_cast<const float4*>(w2)[i];
+                rms_store4(out2 + (size_t)blockIdx.x * d + 4 * (size_t)i,
+                           make_float4(v[k].x * scale * g.x, v[k].y * scale * g.y, v[k].z * scale * g.z, v[k].w * scale * g.w));
+            }
         }
     }
 }
 
-XR_EXPORT int xr_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype, int n, int d,
+// `w2`, `out2` (both or neither): a second norm of the same rows with a weight of its own, written beside the first.
+XR_EXPORT int xr_rmsnorm(const float* x, const int* rows, const float* w, void* out, const float* w2, void* out2, int out_dtype, int n, int d,
                          float eps, cudaStream_t stream) {
-    if (n < 1 || d < 1) return XR_ERR_ARG;
+    if (n < 1 || d < 1 || (w2 == nullptr) != (out2 == nullptr)) return XR_ERR_ARG;
     if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
-    if ((d & 3) == 0 && d <= 32 * 1024 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
+    if ((d & 3) == 0 && d <= 32 * 1024 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)w2 | (uintptr_t)out2) & 15) == 0) {
         int threads = (((d / 4 + 7) / 8 + 31) / 32) * 32;          // eight float4 per thread cover the row
-        if (out_dtype == XR_F32) xr_launch((k_rmsnorm_vec<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, d, eps);
-        else xr_launch((k_rmsnorm_vec<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
+        if (out_dtype == XR_F32) xr_launch((k_rmsnorm_vec<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, w2, (float*)out2, d, eps);
+        else xr_launch((k_rmsnorm_vec<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, d, eps);
         return xr_launch_status();
     }
     int threads = d >= 2048 ? 512 : 256;
-    if (out_dtype == XR_F32) xr_launch((k_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, d, eps);
-    else if (out_dtype == XR_BF16) xr_launch((k_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
+    if (out_dtype == XR_F32) xr_launch((k_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, w2, (float*)out2, d, eps);
+    else if (out_dtype == XR_BF16) xr_launch((k_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, d, eps);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -383,6 +395,10 @@ struct QkNormStoreArgs {
     int pairs;                   // every size, stride and base address is even in elements (set by the launcher)
     int unit;                    // with null weights: divide by the root mean square all the same
     float q_coef; int q_every;   // the queries' factor by position (q_every 0: none)
+    // The projection as the partial sums of a product that was cut along K, [splits][n][cols] float32 (null: `in` holds the rows):
+    // the kernel first sums a row's partials in split order, adds the bias and writes the row to `in`, all `cols` columns (columns
+    // behind the values, such as gates that a later kernel reads, are finished with them).
+    const float* partial; const float* bias; int splits, cols, n;
 };
 
 template <typename T>
@@ -408,14 +424,53 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     __syncthreads();
     xr_pdl_wait();
     const T* row = (const T*)a.in + (size_t)t * a.ld_in;
+    // Rows that are still a product's partial sums: whoever reads a column sums it first (split order, then the bias), rounds it
+    // as the product's own epilogue would and writes it to the row; nobody reads a column that another thread finished.
+    T* wr = (T*)a.in + (size_t)t * a.ld_in;
+    const size_t split_stride = (size_t)a.n * a.cols;
+    const float* psum = a.partial != nullptr ? a.partial + (size_t)t * a.cols : nullptr;
+    auto finished = [&](int c) -> T {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int s2 = 0; s2 < a.splits; s2++) acc += __ldcg(psum + (size_t)s2 * split_stride + c);
+        const T r = xr_from_f32<T>(a.bias ? acc + a.bias[c] : acc);
+        wr[c] = r;
+        return r;
+    };
+    const int part = blockIdx.y, parts = gridDim.y;        // a token's heads and columns may be shared out over several blocks
     const int heads = kdst ? a.H + a.K : a.H;
     // bfloat16 rows whose sizes and strides are even: elements are read and written two at a time
     const bool pairs = sizeof(T) == 2 && a.pairs;
-    for (int head = warp; head < heads; head += nw) {
+    for (int head = part * nw + warp; head < heads; head += parts * nw) {
         const T* src = row + (size_t)head * a.D;
         const float* w = head < a.H ? a.q_w : a.k_w;
         float ss = 0.f;
-        if (pairs) {
+        if (psum != nullptr) {
+            // a lane's columns (up to eight: heads have at most 256 elements), all of a split's loads in flight together
+            float acc[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) acc[k] = 0.f;
+            const float* ph = psum + (size_t)head * a.D + lane;
+#pragma unroll 2
+            for (int s2 = 0; s2 < a.splits; s2++) {
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) v[k] = lane + 32 * k < a.D ? __ldcg(ph + (size_t)s2 * split_stride + 32 * k) : 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; k++) acc[k] += v[k];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int e = lane + 32 * k;
+                if (e < a.D) {
+                    const int c = head * a.D + e;
+                    const T r = xr_from_f32<T>(a.bias ? acc[k] + a.bias[c] : acc[k]);
+                    wr[c] = r;
+                    const float x = xr_to_f32<T>(r);
+                    mine[e] = x; ss = fmaf(x, x, ss);
+                }
+            }
+        } else if (pairs) {
             for (int e = 2 * lane; e < a.D; e += 64) {
                 const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(src) + e));
                 mine[e] = x.x; mine[e + 1] = x.y;
@@ -451,9 +506,19 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
         }
         __syncwarp();
     }
+    const int v_at = (a.H + a.K) * a.D;
+    if (psum != nullptr)                 // columns behind the values (gates that a later kernel reads)
+        for (int c = v_at + a.K * a.Vd + part * blockDim.x + threadIdx.x; c < a.cols; c += parts * blockDim.x) finished(c);
     if (kdst == nullptr) return;
     T* vdst = kdst + a.v_offset;
-    const T* vsrc = row + (size_t)(a.H + a.K) * a.D;
+    const T* vsrc = row + (size_t)v_at;
+    if (psum != nullptr) {
+        for (int i = part * blockDim.x + threadIdx.x; i < a.K * a.hd; i += parts * blockDim.x) {
+            const int kvh = i / a.hd, e = i % a.hd;
+            vdst[(size_t)kvh * head_step + e] = e < a.Vd ? finished(v_at + kvh * a.Vd + e) : xr_from_f32<T>(0.f);
+        }
+        return;
+    }
     if (pairs && !(a.Vd & 1) && !(a.v_offset & 1) && !(((a.H + a.K) * a.D) & 1)) {
         const int hd2 = a.hd >> 1;
         for (int i = threadIdx.x; i < a.K * hd2; i += blockDim.x) {
@@ -474,7 +539,9 @@ XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, 
                                     const int* tok_seg, const int* block_tables, const double* freq, const float* q_w, const float* k_w,
                                     void* cache_k, long long page_stride, long long v_offset, int n, int H, int K, int D, int Vd, int hd,
                                     int rotary_dim, int max_pages, int page_size, int adjacent_pairs, float eps, int unit_norm,
-                                    float q_coef, int q_every, cudaStream_t stream) {
+                                    float q_coef, int q_every, const float* partial, int splits, const float* bias, int cols,
+                                    cudaStream_t stream) {
+    if (partial != nullptr && (splits < 1 || D > 256 || cols < (H + K) * D + K * Vd || cols > ld_in)) return XR_ERR_ARG;
     if (n < 1 || H < 1 || K < 1 || D < 1 || Vd < 1 || hd < D || hd < Vd || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) ||
         page_size < 1 || (rotary_dim > 0 && freq == nullptr) || (q_w == nullptr) != (k_w == nullptr) || q_every < 0 ||
         (unit_norm && q_w != nullptr))
@@ -482,11 +549,13 @@ XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, 
     const int pairs = !((D | hd | ld_in | q_ld | page_stride) & 1) && !(((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)cache_k) & 3);
     QkNormStoreArgs a{in, ld_in, q_out, q_ld, positions, tok_seg, block_tables, freq, q_w, k_w, cache_k, page_stride, v_offset,
                       H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps, pairs, unit_norm ? 1 : 0,
-                      q_coef, q_every};
+                      q_coef, q_every, partial, bias, splits, cols, n};
     const size_t smem = ((size_t)rotary_dim + 8 * (size_t)D) * sizeof(float);
     if (smem > 48 * 1024) return XR_ERR_ARG;
-    if (dtype == XR_F32) xr_launch((k_qk_norm_rope_store<float>), dim3(n), dim3(256), smem, stream, a);
-    else if (dtype == XR_BF16) xr_launch((k_qk_norm_rope_store<__nv_bfloat16>), dim3(n), dim3(256), smem, stream, a);
+    // rows as partial sums come from few tokens: a warp a head over as many blocks as that takes, so that the sums' loads spread
+    const int parts = partial != nullptr ? (H + K + 7) / 8 : 1;
+    if (dtype == XR_F32) xr_launch((k_qk_norm_rope_store<float>), dim3(n, parts), dim3(256), smem, stream, a);
+    else if (dtype == XR_BF16) xr_launch((k_qk_norm_rope_store<__nv_bfloat16>), dim3(n, parts), dim3(256), smem, stream, a);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

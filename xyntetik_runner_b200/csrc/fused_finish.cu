@@ -14,7 +14,7 @@
 template <typename TO>
 __global__ void __launch_bounds__(1024)
 k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
-                     float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+                     float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ w2, TO* __restrict__ out2, int d, float eps) {
     xr_pdl_launch();
     xr_pdl_wait();
     __shared__ float scratch[33];
@@ -53,7 +53,10 @@ k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const
 #pragma unroll
         for (int k = 0; k < FIN_PER; k++) {
             int i = threadIdx.x + k * blockDim.x;
-            if (i < d) o[i] = xr_from_f32<TO>(acc[k] * scale * w[i]);
+            if (i < d) {
+                o[i] = xr_from_f32<TO>(acc[k] * scale * w[i]);
+                if (w2) out2[(size_t)t * d + i] = xr_from_f32<TO>(acc[k] * scale * w2[i]);
+            }
         }
         return;
     }
@@ -69,7 +72,10 @@ k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const
     ss = xr_block_sum(ss, scratch);
     float scale = 1.0f / sqrtf(ss / (float)d + eps);
     __syncthreads();
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
+        if (w2) out2[(size_t)t * d + i] = xr_from_f32<TO>(xr[i] * scale * w2[i]);
+    }
 }
 
 // The same for few tokens: a cluster of FIN_CLUSTER blocks per token, each block owning a contiguous slice of
@@ -93,7 +99,7 @@ __device__ __forceinline__ void fin_cluster_write(float* mine, uint32_t rank, fl
 template <typename TO, int PER>
 __global__ void __launch_bounds__(256)
 k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
-                             float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
+                             float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ w2, TO* __restrict__ out2, int d, int slice, float eps) {
     xr_pdl_launch();
     // "this block runs": its neighbours wait for that before they write into its shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -166,7 +172,10 @@ k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int 
 #pragma unroll
     for (int k = 0; k < PER; k++) {
         int i = c0 + threadIdx.x + k * blockDim.x;
-        if (i < c1) o[i] = xr_from_f32<TO>(acc[k] * scale * wv[k]);
+        if (i < c1) {
+            o[i] = xr_from_f32<TO>(acc[k] * scale * wv[k]);
+            if (w2) out2[(size_t)t * d + i] = xr_from_f32<TO>(acc[k] * scale * w2[i]);
+        }
     }
 }
 
@@ -185,7 +194,7 @@ __device__ __forceinline__ void fin_store4(__nv_bfloat16* o, float4 v) {
 template <typename TO>
 __global__ void __launch_bounds__(1024)
 k_finish_add_rmsnorm_vec4(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
-                          float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+                          float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ w2, TO* __restrict__ out2, int d, float eps) {
     xr_pdl_launch();
     __shared__ float scratch[33];
     const int t = blockIdx.x, quads = d >> 2;
@@ -232,9 +241,15 @@ k_finish_add_rmsnorm_vec4(const float* __restrict__ partial, int splits, int n, 
 #pragma unroll
     for (int k = 0; k < FIN_V4_PER; k++) {
         const int i = threadIdx.x + k * blockDim.x;
-        if (i < quads)
+        if (i < quads) {
             fin_store4(o + 4 * (size_t)i, make_float4(acc[k].x * scale * wv[k].x, acc[k].y * scale * wv[k].y,
                                                        acc[k].z * scale * wv[k].z, acc[k].w * scale * wv[k].w));
+            if (w2) {
+                const float4 g = reinterpret_cast<const float4*>(w2)[i];
+                fin_store4(out2 + (size_t)t * d + 4 * (size_t)i, make_float4(acc[k].x * scale * g.x, acc[k].y * scale * g.y,
+                                                                              acc[k].z * scale * g.z, acc[k].w * scale * g.w));
+            }
+        }
     }
 }
 
@@ -244,7 +259,7 @@ k_finish_add_rmsnorm_vec4(const float* __restrict__ partial, int splits, int n, 
 template <typename TO>
 __global__ void __launch_bounds__(256)
 k_finish_add_rmsnorm_cluster4(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
-                              float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
+                              float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, const float* __restrict__ w2, TO* __restrict__ out2, int d, int slice, float eps) {
     xr_pdl_launch();
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // "this block runs"
     __shared__ float scratch[33];
@@ -290,12 +305,17 @@ k_finish_add_rmsnorm_cluster4(const float* __restrict__ partial, int splits, int
 #pragma unroll
     for (int r = 0; r < FIN_CLUSTER; r++) total += slice_ss[r];
     const float scale = 1.0f / sqrtf(total / (float)d + eps);
-    if (mine)
+    if (mine) {
         fin_store4(out + (size_t)t * d + i, make_float4(a.x * scale * wv.x, a.y * scale * wv.y, a.z * scale * wv.z, a.w * scale * wv.w));
+        if (w2) {
+            const float4 g = *reinterpret_cast<const float4*>(w2 + i);
+            fin_store4(out2 + (size_t)t * d + i, make_float4(a.x * scale * g.x, a.y * scale * g.y, a.z * scale * g.z, a.w * scale * g.w));
+        }
+    }
 }
 
 template <typename TO>
-static int launch_finish_cluster4(const float* partial, int splits, const float* bias, float* x, const float* w, TO* out,
+static int launch_finish_cluster4(const float* partial, int splits, const float* bias, float* x, const float* w, TO* out, const float* w2, TO* out2,
                                   int n, int d, int slice, float eps, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     const int threads = (slice / 4 + 31) / 32 * 32;
@@ -307,12 +327,12 @@ static int launch_finish_cluster4(const float* partial, int splits, const float*
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster4<TO>, partial, splits, n, bias, x, w, out, d, slice, eps);
+    cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster4<TO>, partial, splits, n, bias, x, w, out, w2, out2, d, slice, eps);
     return xr_launch_status();
 }
 
 template <typename TO>
-static int launch_finish_cluster(const float* partial, int splits, const float* bias, float* x, const float* w, TO* out,
+static int launch_finish_cluster(const float* partial, int splits, const float* bias, float* x, const float* w, TO* out, const float* w2, TO* out2,
                                  int n, int d, int slice, float eps, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n * FIN_CLUSTER); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
@@ -323,40 +343,43 @@ static int launch_finish_cluster(const float* partial, int splits, const float* 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
-    if (slice <= 256) cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 1>, partial, splits, n, bias, x, w, out, d, slice, eps);
-    else if (slice <= 512) cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 2>, partial, splits, n, bias, x, w, out, d, slice, eps);
-    else cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 4>, partial, splits, n, bias, x, w, out, d, slice, eps);
+    if (slice <= 256) cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 1>, partial, splits, n, bias, x, w, out, w2, out2, d, slice, eps);
+    else if (slice <= 512) cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 2>, partial, splits, n, bias, x, w, out, w2, out2, d, slice, eps);
+    else cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 4>, partial, splits, n, bias, x, w, out, w2, out2, d, slice, eps);
     return xr_launch_status();
 }
 
+// `w2`, `out2` (both or neither): a second norm of the same row with a weight of its own, written beside the first (a block whose
+// sublayers each have a norm reads the row, and takes its root mean square, once).
 XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const float* bias, float* x, const float* w, void* out,
-                                    int out_dtype, int n, int d, float eps, cudaStream_t stream) {
+                                    const float* w2, void* out2, int out_dtype, int n, int d, float eps, cudaStream_t stream) {
+    if ((w2 == nullptr) != (out2 == nullptr)) return XR_ERR_ARG;
     if (n < 1 || d < 1 || splits < 1) return XR_ERR_ARG;
     if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
     const int slice = (d + FIN_CLUSTER - 1) / FIN_CLUSTER;
-    const bool aligned = (((uintptr_t)partial | (uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
+    const bool aligned = (((uintptr_t)partial | (uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)bias | (uintptr_t)w2 | (uintptr_t)out2) & 15) == 0;
     if (n > 16 && n <= 64 && d >= 512 && (d % (4 * FIN_CLUSTER)) == 0 && d <= 4 * 256 * FIN_CLUSTER && aligned) {
         // 17 to 64 tokens: a cluster of eight blocks per token, each thread one quadruple of its block's slice (measured at
         // width 4096: 5.3 us against 8.4 us for the scalar cluster kernel at 64 tokens; up to 16 tokens the scalar kernel,
         // which is tuned for the latency of a single wave, is the faster one: 4.3 against 4.7 us at 8 tokens)
-        if (out_dtype == XR_F32) return launch_finish_cluster4<float>(partial, splits, bias, x, w, (float*)out, n, d, d / FIN_CLUSTER, eps, stream);
-        return launch_finish_cluster4<__nv_bfloat16>(partial, splits, bias, x, w, (__nv_bfloat16*)out, n, d, d / FIN_CLUSTER, eps, stream);
+        if (out_dtype == XR_F32) return launch_finish_cluster4<float>(partial, splits, bias, x, w, (float*)out, w2, (float*)out2, n, d, d / FIN_CLUSTER, eps, stream);
+        return launch_finish_cluster4<__nv_bfloat16>(partial, splits, bias, x, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, n, d, d / FIN_CLUSTER, eps, stream);
     }
     if (n > 64 && (d & 3) == 0 && d >= 1024 && d <= 4 * FIN_V4_PER * 1024 && aligned) {
         // many tokens: throughput counts, one block of (up to) 1024 threads per token, 16-byte vectors
         int threads = ((d / 4 + FIN_V4_PER - 1) / FIN_V4_PER + 31) / 32 * 32;
         if (threads > 1024) threads = 1024;
-        if (out_dtype == XR_F32) xr_launch((k_finish_add_rmsnorm_vec4<float>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (float*)out, d, eps);
-        else xr_launch((k_finish_add_rmsnorm_vec4<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
+        if (out_dtype == XR_F32) xr_launch((k_finish_add_rmsnorm_vec4<float>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (float*)out, w2, (float*)out2, d, eps);
+        else xr_launch((k_finish_add_rmsnorm_vec4<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, d, eps);
         return xr_launch_status();
     }
     if (n <= 64 && d >= 512 && slice <= FIN_CL_PER * 256) {      // few tokens and a row worth cutting up
-        if (out_dtype == XR_F32) return launch_finish_cluster<float>(partial, splits, bias, x, w, (float*)out, n, d, slice, eps, stream);
-        return launch_finish_cluster<__nv_bfloat16>(partial, splits, bias, x, w, (__nv_bfloat16*)out, n, d, slice, eps, stream);
+        if (out_dtype == XR_F32) return launch_finish_cluster<float>(partial, splits, bias, x, w, (float*)out, w2, (float*)out2, n, d, slice, eps, stream);
+        return launch_finish_cluster<__nv_bfloat16>(partial, splits, bias, x, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, n, d, slice, eps, stream);
     }
     int threads = d >= 4096 ? 1024 : (d >= 1024 ? 512 : 256);      // few tokens, so many threads per token
-    if (out_dtype == XR_F32) xr_launch((k_finish_add_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (float*)out, d, eps);
-    else xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
+    if (out_dtype == XR_F32) xr_launch((k_finish_add_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (float*)out, w2, (float*)out2, d, eps);
+    else xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, d, eps);
     return xr_launch_status();
 }
 

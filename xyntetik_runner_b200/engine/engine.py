@@ -97,8 +97,12 @@ class StepContext:
     # directly calls ``materialize`` first.
     def set_pending(self, x: torch.Tensor, pending) -> None:
         if pending is not None:
-            self.materialize(x)
-            self._pending[x.data_ptr()] = pending
+            # a second sum for the same rows joins the first where their partial sums lie side by side; else the first is taken now
+            before = self._pending.get(x.data_ptr())
+            both = before.join(pending) if before is not None and hasattr(before, "join") else None
+            if both is None:
+                self.materialize(x)
+            self._pending[x.data_ptr()] = both if both is not None else pending
 
     def take_pending(self, x: torch.Tensor):
         return self._pending.pop(x.data_ptr(), None)

@@ -48,14 +48,14 @@ _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 def _declare(L: ctypes.CDLL) -> None:
     sig = {
         "xr_embed": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
-        "xr_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+        "xr_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_act_mul": [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
         "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
         "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
-        "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+        "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
@@ -81,7 +81,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_latent_attention_mma": [_vp, _ll, _ll, _vp, _ll, _i, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
         "xr_heads_gather": [_vp, _ll, _i, _vp, _i, _i, _i, _i, _vp],
         "xr_heads_scatter_gate": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
-        "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
+        "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i,
+                                  _vp, _i, _vp, _i, _vp],
         "xr_rmsnorm_act": [_vp, _i, _ll, _vp, _vp, _ll, _i, _i, _f, _vp],
         "xr_delta": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
         "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _vp],
@@ -158,13 +159,22 @@ def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, feed: Optiona
     _count()
 
 
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
-    """out[i] = x[rows[i] or i] * rsqrt(mean(x^2) + eps) * w; x float32, w float32."""
-    _dev(x, w, out, rows)
+def _second_norm(w2, out2, out, d):
+    assert (w2 is None) == (out2 is None)
+    if w2 is not None:
+        assert w2.dtype == torch.float32 and w2.numel() == d and out2.shape == out.shape and out2.dtype == out.dtype and out2.is_contiguous()
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+            w2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None) -> None:
+    """out[i] = x[rows[i] or i] * rsqrt(mean(x^2) + eps) * w; x float32, w float32.  With `w2`, `out2`: the same rows times a second
+    weight into `out2`, in the same pass (one root mean square for both)."""
+    _dev(x, w, out, rows, w2, out2)
     n, d = out.shape
     assert x.dtype == torch.float32 and w.dtype == torch.float32 and x.shape[1] == d and w.numel() == d
     assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n)
-    _check(lib().xr_rmsnorm(x.data_ptr(), _ptr(rows), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n, d,
+    _second_norm(w2, out2, out, d)
+    _check(lib().xr_rmsnorm(x.data_ptr(), _ptr(rows), w.data_ptr(), out.data_ptr(), _ptr(w2), _ptr(out2), dtype_code(out.dtype), n, d,
                             float(eps), _stream()), "rmsnorm")
     _count()
 
@@ -206,22 +216,27 @@ def rmsnorm_act(inp: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: floa
 def qk_norm_rope_store(inp: torch.Tensor, q_out: torch.Tensor, positions, tok_seg, block_tables, freq: Optional[torch.Tensor],
                        q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], cache_k_ptr: Optional[int], page_stride: int, v_offset: int,
                        H: int, K: int, D: int, Vd: int, hd: int, rotary_dim: int, max_pages: int, page_size: int, adjacent: bool,
-                       eps: float, unit_norm: bool = False, q_coef: float = 0.0, q_every: int = 0) -> None:
+                       eps: float, unit_norm: bool = False, q_coef: float = 0.0, q_every: int = 0, partial: Optional[torch.Tensor] = None,
+                       splits: int = 0, bias: Optional[torch.Tensor] = None) -> None:
     """inp [n, >= (H + K) D + K Vd] (rows may be strided): Q heads, K heads (D each), V heads (Vd each).  Every Q and K head is
     RMS-normed with the weight q_w / k_w (float32 [D], shared by the heads; None: no norm), its first `rotary_dim` elements rotated
     (freq: float64 [rotary_dim / 2]); Q goes to q_out [n, *] (head h at column h * hd), K and V into the token's cache rows, every
     head filled up to `hd` elements with zeros (cache_k_ptr None: nothing is stored).  `unit_norm` (with no weights): every Q
     and K head is divided by its root mean square all the same.  `q_every` > 0: the Q heads of the token at position p are
-    multiplied by 1 + q_coef ln(floor((p + 1) / q_every) + 1)."""
-    _dev(positions, tok_seg, block_tables, freq, q_w, k_w)
+    multiplied by 1 + q_coef ln(floor((p + 1) / q_every) + 1).  `partial` (float32 [splits][n][inp.shape[1]], with `bias`): the rows are
+    still the partial sums of a product cut along K; the kernel sums them (+ bias) into `inp`, every column, before it reads them."""
+    _dev(positions, tok_seg, block_tables, freq, q_w, k_w, partial, bias)
     n = inp.shape[0]
+    assert partial is None or (partial.dtype == torch.float32 and splits >= 1 and partial.numel() >= splits * n * inp.shape[1])
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == inp.shape[1])
     assert inp.stride(1) == 1 and q_out.stride(1) == 1 and inp.dtype == q_out.dtype and q_out.shape[0] == n and q_out.shape[1] >= H * hd
     assert inp.shape[1] >= (H + K) * D + K * Vd and (freq is None or (freq.dtype == torch.float64 and freq.numel() >= rotary_dim // 2))
     assert q_w is None or (q_w.dtype == torch.float32 and k_w.dtype == torch.float32 and q_w.numel() == D and k_w.numel() == D)
     _check(lib().xr_qk_norm_rope_store(inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), q_out.data_ptr(), q_out.stride(0),
                                        positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), _ptr(q_w), _ptr(k_w),
                                        cache_k_ptr, page_stride, v_offset, n, H, K, D, Vd, hd, rotary_dim, max_pages, page_size,
-                                       int(adjacent), float(eps), int(unit_norm), float(q_coef), int(q_every), _stream()),
+                                       int(adjacent), float(eps), int(unit_norm), float(q_coef), int(q_every), _ptr(partial), int(splits),
+                                       _ptr(bias) if partial is not None else None, inp.shape[1], _stream()),
            "qk_norm_rope_store")
     _count()
 
@@ -529,13 +544,15 @@ def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: 
 
 
 def finish_add_rmsnorm(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor], x: torch.Tensor,
-                       w: torch.Tensor, out: torch.Tensor, eps: float) -> None:
-    """x += sum of the split-K partials (+ bias); out = RMSNorm(x) * w.  One pass over each row."""
-    _dev(x, w, out, bias)
+                       w: torch.Tensor, out: torch.Tensor, eps: float, w2: Optional[torch.Tensor] = None,
+                       out2: Optional[torch.Tensor] = None) -> None:
+    """x += sum of the split-K partials (+ bias); out = RMSNorm(x) * w (and out2 = RMSNorm(x) * w2).  One pass over each row."""
+    _dev(x, w, out, bias, w2, out2)
     n, d = x.shape
     assert x.dtype == torch.float32 and w.dtype == torch.float32 and out.shape == (n, d) and partial.numel() >= splits * n * d
-    _check(lib().xr_finish_add_rmsnorm(partial.data_ptr(), splits, _ptr(bias), x.data_ptr(), w.data_ptr(), out.data_ptr(),
-                                       dtype_code(out.dtype), n, d, float(eps), _stream()), "finish_add_rmsnorm")
+    _second_norm(w2, out2, out, d)
+    _check(lib().xr_finish_add_rmsnorm(partial.data_ptr(), splits, _ptr(bias), x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(w2),
+                                       _ptr(out2), dtype_code(out.dtype), n, d, float(eps), _stream()), "finish_add_rmsnorm")
     _count()
 
 

@@ -1,5 +1,5 @@
-"""Prefill and decode throughput of a Turudra or a Besolix model beside a dense Llama of equal size, with the time of every
-kernel family inside the steps (``bench.py --designs``).
+"""Prefill and decode throughput of a Turudra, a Besolix or a Pitolix model beside a dense Llama of equal size, with the time of
+every kernel family inside the steps (``bench.py --designs``).
 
 Sizes resemble real layers; weights are random.  Both models run through the same engine: one prompt of `tokens` tokens
 in one step (prefill), and decode steps of `batch` requests that hold `context` tokens each (``Engine.adopt``: the cache
@@ -21,6 +21,7 @@ import torch
 from . import kernels, measure
 from .config.besolix import BesolixConfig
 from .config.llama import LlamaConfig
+from .config.pitolix import PitolixConfig
 from .config.turudra import TurudraConfig
 from .engine.engine import EngineParams, StepEntry, random_engine
 
@@ -87,6 +88,33 @@ def llama_like_besolix(size: str, positions: int) -> LlamaConfig:
                                   "max_position_embeddings": positions, "sliding_window": at["window"], "torch_dtype": "bfloat16"})
 
 
+PITOLIX_SIZES = {
+    # name: (width, heads, kv heads, head size, rotated elements, positions per step of the query factor, feed-forward, vocab); four
+    # layers (rotary, sink, rotary, sink) of which the middle two run twice: six layer runs
+    "pitolix-w1024": (1024, 8, 2, 128, 64, 512, 2816, 32000),
+    "pitolix-w2048": (2048, 16, 4, 128, 64, 1024, 5632, 32000),
+}
+
+
+def pitolix_config(size: str) -> PitolixConfig:
+    W, H, K, D, rot, every, ff, vocab = PITOLIX_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    sizes = {"heads": H, "kv_heads": K, "dim": D, "vdim": D, "scale": D ** -0.5}
+    rotary = {"type": "attention_2", "mlp": mlp, "mixer": dict(sizes, rot={"base": 10000.0, "dims": rot})}
+    sink = {"type": "attention", "mlp": mlp, "mixer": dict(sizes, q_temp={"coef": 0.1, "every": every})}
+    return PitolixConfig.from_dict({"architecture": "Pitolix", "vocab": vocab, "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+                                    "layers": [rotary, sink, rotary, sink], "loop": {"start": 1, "stop": 3, "times": 2}})
+
+
+def llama_like_pitolix(size: str, positions: int) -> LlamaConfig:
+    """A dense decoder of the same width, number of layer runs, heads and feed-forward."""
+    W, H, K, D, rot, every, ff, vocab = PITOLIX_SIZES[size]
+    return LlamaConfig.from_dict({"architectures": ["LlamaForCausalLM"], "hidden_size": W, "num_hidden_layers": 6,
+                                  "num_attention_heads": H, "num_key_value_heads": K, "head_dim": D,
+                                  "intermediate_size": ff, "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+                                  "max_position_embeddings": positions, "torch_dtype": "bfloat16"})
+
+
 FAMILIES = {
     "gemm_tc": "products (tcgen05)", "gemm_tc_deferred": "products (tcgen05)", "gemm_simt": "products (FMA)",
     "finish_plain": "products (tcgen05)", "finish_add_rmsnorm": "norms", "rmsnorm": "norms", "finish_rope_store": "rotation + cache store",
@@ -98,6 +126,7 @@ FAMILIES = {
     "mlstm": "mlstm recurrence", "route_topk": "routing", "moe_plan": "routing", "moe_gemm": "experts' products", "moe_combine": "experts' sum",
     "delta": "delta recurrence", "head_norm_gate": "delta recurrence", "qk_norm_rope_store": "rotation + cache store",
     "rmsnorm_act": "norms",
+    "sigmoid_gate": "output gates", "stream_step": "stream kernels",
     "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
 }
 
@@ -198,7 +227,36 @@ def _llama_work(cfg, tokens, keys_per_token, decode):
     per_layer = W * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * W + 3 * W * cfg.intermediate_size
     fl_p = 2.0 * tokens * (per_layer * L + cfg.vocab_size * W * (1 if decode else 1.0 / tokens))
     by_p = 2.0 * (per_layer * L + cfg.vocab_size * W)
-    return {"attention": (fl_a, by_a), "products (tcgen05)": (fl_p, by_p)}
+    # the memory-bound kernels between the products: a norm reads a float32 row and writes an activation row; the rotation
+    # reads the projection's rows, writes the queries back and the keys and values into their pages
+    by_n = tokens * W * (4 + 2) * (2 * L + 1)
+    by_r = tokens * 2.0 * 2 * (cfg.q_dim + 2 * cfg.kv_dim) * L
+    return {"attention": (fl_a, by_a), "products (tcgen05)": (fl_p, by_p), "norms": (0.0, by_n), "rotation + cache store": (0.0, by_r)}
+
+
+def _pitolix_work(cfg, tokens, keys_per_token, decode):
+    """(FLOPs, bytes) per kernel family in one step of `tokens` tokens, counted like ``_llama_work``."""
+    W = cfg.width
+    fl_a = by_a = fl_p = by_p = by_n = by_r = by_g = 0.0
+    for i, _ in cfg.layer_runs():
+        lay = cfg.layers[i]
+        m = lay.mixer
+        hd = max(m.dim, m.vdim)
+        gate = m.heads * m.vdim if m.kind == "attention" else m.heads
+        cols = (m.heads + m.kv_heads) * m.dim + m.kv_heads * m.vdim + gate
+        per_layer = W * cols + m.heads * m.vdim * W + (3 * W * lay.mlp.ff if lay.mlp is not None else 0)
+        fl_a += 2.0 * tokens * m.heads * keys_per_token * (m.dim + m.vdim)
+        by_a += (tokens if decode else 1) * keys_per_token * 2 * m.kv_heads * hd * 2
+        fl_p += 2.0 * tokens * per_layer
+        by_p += 2.0 * per_layer         # (every run of a looped layer reads its weights again: the layers between exceed the L2 cache)
+        by_n += tokens * W * (4 + 2 * (2 if lay.mlp is not None else 1))
+        by_r += tokens * 2.0 * ((cols - gate) + (m.heads + 2 * m.kv_heads) * hd)
+        by_g += tokens * 2.0 * (2 * m.heads * m.vdim + gate)
+    fl_p += 2.0 * cfg.vocab * W * (tokens if decode else 1)
+    by_p += 2.0 * cfg.vocab * W
+    by_n += tokens * W * (4 + 2)
+    return {"attention": (fl_a, by_a), "products (tcgen05)": (fl_p, by_p), "norms": (0.0, by_n), "rotation + cache store": (0.0, by_r),
+            "output gates": (0.0, by_g)}
 
 
 def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: int, warmup: int, pk, phase: str = "both") -> dict:
@@ -287,14 +345,16 @@ def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, 
     pool = batch * (context + 64 * (2 + (steps + warmup + 8) // 64)) + tokens + 64
     ep = lambda: EngineParams(dtype="bfloat16", max_tokens=pool, page_size=64, max_requests=batch + 1,
                               max_request_tokens=max(tokens, context + steps + warmup + 72), max_step_tokens=tokens)
-    if size in BESOLIX_SIZES:
+    if size in PITOLIX_SIZES:
+        arms = (("pitolix", pitolix_config(size), _pitolix_work), ("llama", llama_like_pitolix(size, context + tokens), _llama_work))
+    elif size in BESOLIX_SIZES:
         arms = (("besolix", besolix_config(size), _besolix_work), ("llama", llama_like_besolix(size, context + tokens), _llama_work))
     else:
         tcfg = turudra_config(size)
         arms = (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work))
     for name, cfg, work in arms:
         # (`models` names arms to run; "turudra" also stands for the new design's arm of a Besolix size: the default runs both arms)
-        if name not in models and not (name == "besolix" and "turudra" in models):
+        if name not in models and not (name in ("besolix", "pitolix") and "turudra" in models):
             continue
         t0 = time.perf_counter()
         eng = random_engine(cfg, 5, ep())

@@ -184,11 +184,16 @@ class GQAAttention(Mixer):
             gate_at = (self.H + self.K) * self.D + self.K * self.Vd
             cols = gate_at + self.gate_cols
             proj = ctx.buf("attn_proj", (n, -(-cols // 8) * 8), ctx.act_dtype)[:, :cols]
-            self.qkv.forward(h, proj)
+            # (a product that was cut along K leaves its partial sums to the same kernel)
+            pend = self.qkv.forward(h, proj, defer=True)
             coef, every = self.q_temp if self.q_temp is not None else (0.0, 0)
             kernels.qk_norm_rope_store(proj, qkv, ctx.positions, ctx.tok_seg, bt, self.freq64, self.q_norm_w, self.k_norm_w, store_ptr,
                                        page_stride, v_offset, self.H, self.K, self.D, self.Vd, self.hd, rot_dim, ctx.max_pages,
-                                       ctx.page_size, adjacent, self.norm_eps, self.unit_norm, coef, every)
+                                       ctx.page_size, adjacent, self.norm_eps, self.unit_norm, coef, every,
+                                       partial=None if pend is None else pend.partial, splits=0 if pend is None else pend.splits,
+                                       bias=None if pend is None else pend.bias)
+            if pend is not None:
+                pend.release()
         else:
             pend = self.qkv.forward(h, qkv, defer=True)
             if pend is not None and lay.writes_cache:

@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from .base import Block, FeedForward, Mixer, Norm, register_block
+from .norm import RMSNorm
 
 
 class PreNormBlock(Block):
@@ -88,12 +89,18 @@ class ParallelBlock(Block):
         from .. import kernels
         n, width = x.shape
         h = ctx.buf("block_normed", (n, width), ctx.act_dtype)
-        self.norm.forward(ctx, x, h)
         h2 = h
-        if self.ff_norm is not None:
-            # the second norm reads the x the first one read, before any sublayer adds to it
+        if self.ff_norm is None:
+            self.norm.forward(ctx, x, h)
+        else:
+            # the second norm reads the x the first one reads, before any sublayer adds to it: one kernel takes the row's root
+            # mean square once and writes both
             h2 = ctx.buf("block_normed_ff", (n, width), ctx.act_dtype)
-            self.ff_norm.forward(ctx, x, h2)
+            if isinstance(self.norm, RMSNorm) and isinstance(self.ff_norm, RMSNorm) and self.norm.eps == self.ff_norm.eps:
+                self.norm.forward(ctx, x, h, second=self.ff_norm, out2=h2)
+            else:
+                self.norm.forward(ctx, x, h)
+                self.ff_norm.forward(ctx, x, h2)
         if self.direct:
             self.mixer.forward(ctx, h, x, lay)
             if self.feed_forward is not None:

@@ -27,6 +27,33 @@ class Pending:
         kernels.finish_plain(self.partial, self.splits, self.bias, self.out, self.accumulate)
         self.release()
 
+    def join(self, later: "Pending") -> Optional["Pending"]:
+        """One pending sum for this product's and a later one's, when both add into the same rows, their slabs lie one right
+        behind the other and at most one has a bias: the partial sums then read as one array [splits + later.splits][n][width],
+        summed in that order by one kernel.  (Side-by-side sublayers that add into the stream one after the other leave such a
+        pair.)  None when they do not join."""
+        if not (isinstance(later, Pending) and self.accumulate and later.accumulate and self.out.data_ptr() == later.out.data_ptr()
+                and self.out.shape == later.out.shape and (self.bias is None or later.bias is None)):
+            return None
+        if later.partial.data_ptr() != self.partial.data_ptr() + 4 * self.partial.numel():
+            return None
+        return _Joined(self, later)
+
+
+class _Joined(Pending):
+    def __init__(self, first: Pending, second: Pending):
+        ws = first.sums._ws
+        at = (first.partial.data_ptr() - ws.scratch.data_ptr()) // 4
+        self.parts = (first, second)
+        self.partial = ws.scratch[at:at + first.partial.numel() + second.partial.numel()]
+        self.splits = first.splits + second.splits
+        self.bias = first.bias if first.bias is not None else second.bias
+        self.out, self.accumulate = first.out, True
+
+    def release(self) -> None:
+        for p in self.parts:
+            p.release()
+
 
 def usable(lin, x, out, accumulate) -> bool:
     return ENABLED and lin.weight is not None and kernels.gemm_tc_supported(x, lin.weight, out)

@@ -27,16 +27,22 @@ class RMSNorm(Norm):
     def weight_bytes(self):
         return self.width * 4
 
-    def forward(self, ctx, x, out, rows=None):
+    def forward(self, ctx, x, out, rows=None, second=None, out2=None):
+        """`second` (another RMSNorm of the same width and eps) with `out2`: both norms of the same rows in one kernel."""
+        w2 = None
+        if second is not None:
+            if second.eps != self.eps or second.width != self.width:
+                raise ValueError(f"{self.name} and {second.name}: two norms share a pass only with the same width and eps")
+            w2 = second.weight
         pend = ctx.take_pending(x)
         if pend is not None and rows is None:
             # the product before this norm left partial sums: sum, add into x and normalise in one pass
-            kernels.finish_add_rmsnorm(pend.partial, pend.splits, pend.bias, x, self.weight, out, self.eps)
+            kernels.finish_add_rmsnorm(pend.partial, pend.splits, pend.bias, x, self.weight, out, self.eps, w2, out2)
             pend.release()
             return
         if pend is not None:
             pend.finish()
-        kernels.rmsnorm(x, self.weight, out, self.eps, rows)
+        kernels.rmsnorm(x, self.weight, out, self.eps, rows, w2, out2)
 
 
 register_norm("rmsnorm", RMSNorm)
