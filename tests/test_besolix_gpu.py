@@ -195,7 +195,10 @@ def test_norm_rotation_and_store_kernel(dtype, adjacent):
     from xyntetik_runner_b200 import kernels
     torch.manual_seed(5)
     dev = "cuda"
-    for H, K, D, Vd, rot in ((3, 1, 12, 20, 6), (2, 2, 16, 16, 16), (4, 2, 40, 8, 0), (1, 1, 6, 70, 4)):
+    # (the later sizes fall on 16-byte borders, which bfloat16 rows take eight elements a lane: 4, 8, 16 and 32 lanes a head, heads
+    # that do not fill the last warp, values longer and shorter than keys, a rotation over part of a head and over all of it)
+    for H, K, D, Vd, rot in ((3, 1, 12, 20, 6), (2, 2, 16, 16, 16), (4, 2, 40, 8, 0), (1, 1, 6, 70, 4), (9, 3, 24, 8, 16), (5, 2, 64, 128, 32),
+                             (3, 1, 128, 64, 128), (4, 4, 48, 96, 16), (2, 1, 256, 8, 64), (7, 1, 32, 32, 0), (16, 4, 128, 128, 64)):
         hd = -(-max(D, Vd) // 16) * 16
         n, page, max_pages = 9, 4, 8
         cols = (H + K) * D + K * Vd

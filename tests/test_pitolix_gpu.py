@@ -193,7 +193,9 @@ def test_unit_heads_query_factor_and_store_kernel(dtype):
     from xyntetik_runner_b200 import kernels
     torch.manual_seed(5)
     dev = "cuda"
-    for H, K, D, Vd, coef, every in ((3, 1, 12, 20, 0.7, 4), (2, 2, 16, 16, 0.3, 1), (4, 2, 40, 8, 0.0, 0), (1, 1, 6, 70, 2.0, 29), (14, 7, 36, 16, 0.3, 8)):
+    # (the later sizes fall on 16-byte borders, which bfloat16 rows take eight elements a lane: 4, 8, 16 and 32 lanes a head)
+    for H, K, D, Vd, coef, every in ((3, 1, 12, 20, 0.7, 4), (2, 2, 16, 16, 0.3, 1), (4, 2, 40, 8, 0.0, 0), (1, 1, 6, 70, 2.0, 29), (14, 7, 36, 16, 0.3, 8),
+                                     (9, 3, 24, 8, 0.5, 2), (5, 2, 64, 128, 0.3, 5), (3, 3, 96, 96, 1.0, 3), (2, 1, 256, 8, 0.2, 28), (16, 4, 128, 128, 0.1, 6)):
         hd = -(-max(D, Vd) // 16) * 16
         n, page, max_pages = 9, 4, 8
         cols = (H + K) * D + K * Vd

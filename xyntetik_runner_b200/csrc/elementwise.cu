@@ -405,15 +405,17 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 k_qk_norm_rope_store(QkNormStoreArgs a) {
     xr_pdl_launch();
-    extern __shared__ float qk_sm[];                   // [half] cosines, [half] sines, then D floats per warp
+    extern __shared__ __align__(16) float qk_sm[];     // [half] cosines, [half] sines, then D floats per warp
     const int t = blockIdx.x, half = a.rotary_dim >> 1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int pos = a.positions[t];
     float* cs = qk_sm;
     float* mine = qk_sm + 2 * half + (size_t)warp * a.D;
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
-    }
+    const int part = blockIdx.y, parts = gridDim.y;        // a token's heads and columns may be shared out over several blocks
+    if (part * nw < a.H + a.K)                             // (a block that only finishes columns behind the heads needs no angles)
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
+        }
     T* kdst = nullptr;
     if (a.cache_k != nullptr) {
         const int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
@@ -431,17 +433,18 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     const float* psum = a.partial != nullptr ? a.partial + (size_t)t * a.cols : nullptr;
     auto finished = [&](int c) -> T {
         float acc = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int s2 = 0; s2 < a.splits; s2++) acc += __ldcg(psum + (size_t)s2 * split_stride + c);
         const T r = xr_from_f32<T>(a.bias ? acc + a.bias[c] : acc);
         wr[c] = r;
         return r;
     };
-    const int part = blockIdx.y, parts = gridDim.y;        // a token's heads and columns may be shared out over several blocks
     const int heads = kdst ? a.H + a.K : a.H;
     // bfloat16 rows whose sizes and strides are even: elements are read and written two at a time
     const bool pairs = sizeof(T) == 2 && a.pairs;
-    for (int head = part * nw + warp; head < heads; head += parts * nw) {
+    // with more blocks than the heads take, the first ones take the heads and the others the columns behind them
+    const int head_parts = min(parts, (heads + nw - 1) / nw), tail_parts = parts - head_parts;
+    for (int head = part * nw + warp; head < heads && part < head_parts; head += head_parts * nw) {
         const T* src = row + (size_t)head * a.D;
         const float* w = head < a.H ? a.q_w : a.k_w;
         float ss = 0.f;
@@ -451,7 +454,7 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
 #pragma unroll
             for (int k = 0; k < 8; k++) acc[k] = 0.f;
             const float* ph = psum + (size_t)head * a.D + lane;
-#pragma unroll 2
+#pragma unroll 8
             for (int s2 = 0; s2 < a.splits; s2++) {
                 float v[8];
 #pragma unroll
@@ -507,18 +510,22 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
         __syncwarp();
     }
     const int v_at = (a.H + a.K) * a.D;
-    if (psum != nullptr)                 // columns behind the values (gates that a later kernel reads)
-        for (int c = v_at + a.K * a.Vd + part * blockDim.x + threadIdx.x; c < a.cols; c += parts * blockDim.x) finished(c);
-    if (kdst == nullptr) return;
-    T* vdst = kdst + a.v_offset;
-    const T* vsrc = row + (size_t)v_at;
     if (psum != nullptr) {
-        for (int i = part * blockDim.x + threadIdx.x; i < a.K * a.hd; i += parts * blockDim.x) {
-            const int kvh = i / a.hd, e = i % a.hd;
+        // the columns behind the values (gates that a later kernel reads), then the values, a thread a column
+        const int behind = a.cols - v_at - a.K * a.Vd, n_v = kdst ? a.K * a.hd : 0;
+        T* vdst = kdst ? kdst + a.v_offset : nullptr;
+        if (tail_parts > 0 && part < head_parts) return;
+        const int first = tail_parts > 0 ? part - head_parts : part, step = (tail_parts > 0 ? tail_parts : parts) * blockDim.x;
+        for (int i = first * blockDim.x + threadIdx.x; i < behind + n_v; i += step) {
+            if (i < behind) { finished(v_at + a.K * a.Vd + i); continue; }
+            const int kvh = (i - behind) / a.hd, e = (i - behind) % a.hd;
             vdst[(size_t)kvh * head_step + e] = e < a.Vd ? finished(v_at + kvh * a.Vd + e) : xr_from_f32<T>(0.f);
         }
         return;
     }
+    if (kdst == nullptr) return;
+    T* vdst = kdst + a.v_offset;
+    const T* vsrc = row + (size_t)v_at;
     if (pairs && !(a.Vd & 1) && !(a.v_offset & 1) && !(((a.H + a.K) * a.D) & 1)) {
         const int hd2 = a.hd >> 1;
         for (int i = threadIdx.x; i < a.K * hd2; i += blockDim.x) {
@@ -532,6 +539,117 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     for (int i = threadIdx.x; i < a.K * a.hd; i += blockDim.x) {
         const int kvh = i / a.hd, e = i % a.hd;
         vdst[(size_t)kvh * head_step + e] = e < a.Vd ? vsrc[(size_t)kvh * a.Vd + e] : xr_from_f32<T>(0.f);
+    }
+}
+
+// The same for bfloat16 rows of whole prompts when every size, stride and address falls on a 16-byte border.  A block brings its
+// token's row (queries, keys, values) into shared memory, 16 bytes a thread and all loads in flight together; then SUB lanes share a
+// head, eight consecutive elements a lane (SUB * 8 >= hd), so that a warp takes 32 / SUB heads at a time: one 16-byte read, the sum
+// of squares over the SUB lanes by shuffles, the rotation's partner as a second 16-byte read of the row, one 16-byte store.
+template <int SUB>
+__global__ void __launch_bounds__(256)
+k_qk_norm_rope_store_vec(QkNormStoreArgs a) {
+    xr_pdl_launch();
+    extern __shared__ __align__(16) float qk_sm[];     // [half] cosines, [half] sines, then (on a 16-byte border) the row
+    const int t = blockIdx.x, half = a.rotary_dim >> 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int pos = a.positions[t];
+    float* cs = qk_sm;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
+    __nv_bfloat16* kdst = nullptr;
+    if (a.cache_k != nullptr) {
+        const int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
+        kdst = (__nv_bfloat16*)a.cache_k + (size_t)page * a.page_stride + (size_t)(pos % a.page_size) * a.hd;
+    }
+    const size_t head_step = (size_t)a.page_size * a.hd;
+    const float q_factor = a.q_every > 0 ? 1.0f + a.q_coef * logf((float)((pos + 1) / a.q_every) + 1.0f) : 1.0f;
+    const int v_at = (a.H + a.K) * a.D;
+    Bf16x8* staged = reinterpret_cast<Bf16x8*>(qk_sm + ((2 * half + 3) & ~3));
+    xr_pdl_wait();
+    {
+        const Bf16x8* g = reinterpret_cast<const Bf16x8*>((const __nv_bfloat16*)a.in + (size_t)t * a.ld_in);
+        const int n16 = (v_at + a.K * a.Vd) >> 3;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) staged[i] = g[i];
+    }
+    __syncthreads();
+    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(staged);
+    const int heads = kdst ? a.H + a.K : a.H;
+    const int e0 = (lane & (SUB - 1)) << 3;
+    const bool normed = a.q_w != nullptr || a.unit;
+    for (int h0 = warp * (32 / SUB); h0 < heads; h0 += nw * (32 / SUB)) {
+        const int head = h0 + lane / SUB;
+        const bool live = head < heads && e0 < a.D;
+        float x[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) x[k] = 0.f;
+        if (live) {
+            const Bf16x8 v = *reinterpret_cast<const Bf16x8*>(row + (size_t)head * a.D + e0);
+#pragma unroll
+            for (int k = 0; k < 4; k++) { const float2 f = __bfloat1622float2(v.p[k]); x[2 * k] = f.x; x[2 * k + 1] = f.y; }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) ss = fmaf(x[k], x[k], ss);
+#pragma unroll
+        for (int o = SUB >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (head >= heads || e0 >= a.hd) continue;
+        float inv = normed ? 1.0f / sqrtf(ss / (float)a.D + a.eps) : 1.0f;
+        if (head < a.H) inv *= q_factor;
+        const float* w = head < a.H ? a.q_w : a.k_w;
+        float y[8];
+        if (w != nullptr && live) {
+            const float4 w0 = *reinterpret_cast<const float4*>(w + e0), w1 = *reinterpret_cast<const float4*>(w + e0 + 4);
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int k = 0; k < 8; k++) y[k] = x[k] * inv * ww[k];
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; k++) y[k] = x[k] * inv;
+        }
+        if (live && e0 < a.rotary_dim) {
+            if (a.adjacent) {
+                const int j0 = e0 >> 1;
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float c = cs[j0 + k], sn = cs[half + j0 + k], u = y[2 * k], v = y[2 * k + 1];
+                    y[2 * k] = u * c - v * sn;
+                    y[2 * k + 1] = v * c + u * sn;
+                }
+            } else {
+                const bool first = e0 < half;
+                const int other = first ? e0 + half : e0 - half, j0 = first ? e0 : e0 - half;
+                const Bf16x8 v = *reinterpret_cast<const Bf16x8*>(row + (size_t)head * a.D + other);
+                float z[8];
+#pragma unroll
+                for (int k = 0; k < 4; k++) { const float2 f = __bfloat1622float2(v.p[k]); z[2 * k] = f.x * inv; z[2 * k + 1] = f.y * inv; }
+                if (w != nullptr) {
+#pragma unroll
+                    for (int k = 0; k < 8; k++) z[k] *= w[other + k];
+                }
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const float c = cs[j0 + k], sn = cs[half + j0 + k];
+                    y[k] = first ? y[k] * c - z[k] * sn : y[k] * c + z[k] * sn;
+                }
+            }
+        }
+        Bf16x8 out;
+#pragma unroll
+        for (int k = 0; k < 4; k++) out.p[k] = __floats2bfloat162_rn(y[2 * k], y[2 * k + 1]);
+        __nv_bfloat16* dst = head < a.H ? (__nv_bfloat16*)a.q_out + (size_t)t * a.q_ld + (size_t)head * a.hd : kdst + (size_t)(head - a.H) * head_step;
+        *reinterpret_cast<Bf16x8*>(dst + e0) = out;
+    }
+    if (kdst == nullptr) return;
+    __nv_bfloat16* vdst = kdst + a.v_offset;
+    const int hd8 = a.hd >> 3;
+    for (int i = threadIdx.x; i < a.K * hd8; i += blockDim.x) {
+        const int kvh = i / hd8, e = (i % hd8) << 3;
+        Bf16x8 v;
+#pragma unroll
+        for (int k = 0; k < 4; k++) v.p[k] = __floats2bfloat162_rn(0.f, 0.f);
+        if (e < a.Vd) v = *reinterpret_cast<const Bf16x8*>(row + (size_t)v_at + (size_t)kvh * a.Vd + e);
+        *reinterpret_cast<Bf16x8*>(vdst + (size_t)kvh * head_step + e) = v;
     }
 }
 
@@ -552,8 +670,27 @@ XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, 
                       q_coef, q_every, partial, bias, splits, cols, n};
     const size_t smem = ((size_t)rotary_dim + 8 * (size_t)D) * sizeof(float);
     if (smem > 48 * 1024) return XR_ERR_ARG;
-    // rows as partial sums come from few tokens: a warp a head over as many blocks as that takes, so that the sums' loads spread
-    const int parts = partial != nullptr ? (H + K + 7) / 8 : 1;
+    // bfloat16 rows of whole prompts whose sizes, strides and addresses all fall on 16-byte borders: eight elements a lane
+    const int row_cols = (H + K) * D + K * Vd;
+    const size_t vec_smem = (((size_t)rotary_dim * sizeof(float) + 15) & ~(size_t)15) + (size_t)row_cols * 2;
+    const int rot_ok = adjacent_pairs ? !(rotary_dim & 7) : !(rotary_dim & 15);
+    if (dtype == XR_BF16 && partial == nullptr && rot_ok && hd <= 256 && vec_smem <= 48 * 1024 &&
+        !((D | Vd | hd | ld_in | q_ld | page_stride | v_offset) & 7) &&
+        !(((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)cache_k | (uintptr_t)q_w | (uintptr_t)k_w) & 15)) {
+        if (hd <= 32) xr_launch((k_qk_norm_rope_store_vec<4>), dim3(n), dim3(256), vec_smem, stream, a);
+        else if (hd <= 64) xr_launch((k_qk_norm_rope_store_vec<8>), dim3(n), dim3(256), vec_smem, stream, a);
+        else if (hd <= 128) xr_launch((k_qk_norm_rope_store_vec<16>), dim3(n), dim3(256), vec_smem, stream, a);
+        else xr_launch((k_qk_norm_rope_store_vec<32>), dim3(n), dim3(256), vec_smem, stream, a);
+        return xr_launch_status();
+    }
+    // rows as partial sums come from few tokens: a warp a head, a thread a column behind the heads (values, gates), over as many
+    // blocks as that takes, so that the sums' loads spread and no thread sums more than one column after the other
+    int parts = 1;
+    if (partial != nullptr) {
+        const int behind = cols - (H + K) * D - K * Vd + K * hd;
+        parts = (H + K + 7) / 8 + (behind + 255) / 256;
+        if (parts > 64) parts = 64;
+    }
     if (dtype == XR_F32) xr_launch((k_qk_norm_rope_store<float>), dim3(n, parts), dim3(256), smem, stream, a);
     else if (dtype == XR_BF16) xr_launch((k_qk_norm_rope_store<__nv_bfloat16>), dim3(n, parts), dim3(256), smem, stream, a);
     else return XR_ERR_ARG;
