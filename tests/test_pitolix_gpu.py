@@ -250,14 +250,16 @@ def test_output_gate_kernel(dtype):
     wider array."""
     from xyntetik_runner_b200 import kernels
     torch.manual_seed(6)
-    for H, hd, Vd in ((3, 32, 20), (8, 96, 96), (1, 16, 5), (5, 64, 64)):
+    # (gates that start at column 16 of rows of a multiple of eight elements are on 16-byte borders: eight elements a thread)
+    for H, hd, Vd, at, behind in ((3, 32, 20, 11, 3), (8, 96, 96, 11, 3), (1, 16, 5, 11, 3), (5, 64, 64, 11, 3), (8, 96, 96, 16, 0), (5, 64, 64, 16, 8),
+                                  (4, 128, 64, 16, 0), (3, 32, 24, 8, 0)):
         n = 7
         for each in (True, False):
             o = torch.randn(n, H * hd).to(dtype)
-            wide = torch.randn(n, 11 + (H * Vd if each else H) + 3).to(dtype)
-            g = wide[:, 11:11 + (H * Vd if each else H)]
+            wide = torch.randn(n, at + (H * Vd if each else H) + behind).to(dtype)
+            g = wide[:, at:at + (H * Vd if each else H)]
             od, wd = o.cuda(), wide.cuda()
-            kernels.sigmoid_gate(od, wd[:, 11:11 + g.shape[1]], H, hd, Vd, each)
+            kernels.sigmoid_gate(od, wd[:, at:at + g.shape[1]], H, hd, Vd, each)
             s = torch.sigmoid(g.double())
             want = o.double().view(n, H, hd).clone()
             want[:, :, :Vd] *= s.view(n, H, Vd) if each else s.view(n, H, 1)
@@ -509,6 +511,29 @@ def test_drawn_configurations(seed):
                 for rid in reqs:
                     close(got[rid], ref[rid], dtype, f"drawn {seed}/{cut}/{dtype}/{rid}: {cfg['layers']} {cfg['loop']}", cfg, t, reqs[rid],
                           ("drawn", seed, rid))
+
+
+def test_wide_heads_and_long_prompts():
+    """Heads of 80 to 256 elements (values of 48 to 256), 20 heads over one key head, a rotation over the whole head, a loop over three
+    layers, prompts of several hundred tokens: whole, with a decoded tail and in mixed batches, in both precisions."""
+    cfg = tp.model(1000, 320, 1e-5, [
+        tp.layer(tp.sink_attention(10, 5, 80, 112, 0.11, 0.3, 256), 640),
+        tp.layer(tp.rotary_attention(12, 3, 160, 64, 0.08, 10000.0, 80), 512),
+        tp.layer(tp.sink_attention(6, 6, 192, 192, 0.07, 0.5, 100), None),
+        tp.layer(tp.rotary_attention(4, 1, 256, 256, 0.0625, 500000.0, 256), 256),
+        tp.layer(tp.rotary_attention(20, 1, 32, 48, 0.17, 100.0, 16), 384)], loop=(1, 4, 2), embedding_scale=16.0)
+    t = tp.draw(cfg, 77)
+    reqs = {f"r{i}": traces.random_tokens(31 * i + 5, n, cfg["vocab"]) for i, n in enumerate((700, 3, 260, 129))}
+    ref = {rid: tp.plain_logits(cfg, t, toks) for rid, toks in reqs.items()}
+    with tempfile.TemporaryDirectory() as tmp:
+        path, _, _ = tp.make_folder(tmp, None, t, cfg)
+        for dtype in ("float32", "bfloat16"):
+            for cut in ("whole", "tail", "mixed"):
+                steps = CUTS[cut](reqs)
+                res, _ = run(path, dtype, steps, 64)
+                got = traces.collect(steps, res, cfg["vocab"])
+                for rid in reqs:
+                    close(got[rid], ref[rid], dtype, f"wide/{cut}/{dtype}/{rid}", cfg, t, reqs[rid], ("wide", rid))
 
 
 # ---- through the entry points --------------------------------------------------------------------------------------------

@@ -811,7 +811,8 @@ XR_EXPORT int xr_stream_step(float* x, const float* x0, const float* v, int n, i
 // ---------------------------------------------------------------------------
 // An output gate on attention heads: o[t][h][d] *= sigmoid(g[t][h * Vd + d]) (a gate per element, `each`) or
 // sigmoid(g[t][h]) (a gate per head), for d < Vd of every head's hd columns; the sigmoid and the product in float32.
-// g are columns of the projection's rows (row stride ld_g).  Two elements a thread where the sizes are even.
+// g are columns of the projection's rows (row stride ld_g).  bfloat16: eight elements a thread where sizes, strides and addresses
+// fall on 16-byte borders (`two` = 8), two where they are even (`two` = 2).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void k_sigmoid_gate(T* __restrict__ o, long long ld_o, const T* __restrict__ g, long long ld_g, int H, int hd, int Vd, int each, int two) {
@@ -820,6 +821,31 @@ __global__ void k_sigmoid_gate(T* __restrict__ o, long long ld_o, const T* __res
     const int t = blockIdx.x;
     T* orow = o + (size_t)t * ld_o;
     const T* grow = g + (size_t)t * ld_g;
+    if (sizeof(T) == 2 && two == 8) {
+        const int v8 = Vd >> 3, per = H * v8;
+        for (int i = threadIdx.x; i < per; i += blockDim.x) {
+            const int h = i / v8, d = (i % v8) << 3;
+            Bf16x8* dst = reinterpret_cast<Bf16x8*>(reinterpret_cast<__nv_bfloat16*>(orow) + (size_t)h * hd + d);
+            Bf16x8 x = *dst;
+            if (each) {
+                const Bf16x8 gg = *reinterpret_cast<const Bf16x8*>(reinterpret_cast<const __nv_bfloat16*>(grow) + (size_t)h * Vd + d);
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float2 a = __bfloat1622float2(x.p[k]), b = __bfloat1622float2(gg.p[k]);
+                    x.p[k] = __floats2bfloat162_rn(a.x / (1.0f + expf(-b.x)), a.y / (1.0f + expf(-b.y)));
+                }
+            } else {
+                const float den = 1.0f + expf(-xr_to_f32<T>(grow[h]));
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float2 a = __bfloat1622float2(x.p[k]);
+                    x.p[k] = __floats2bfloat162_rn(a.x / den, a.y / den);
+                }
+            }
+            *dst = x;
+        }
+        return;
+    }
     if (sizeof(T) == 2 && two) {
         const int half_v = Vd >> 1, per = H * half_v;
         for (int i = threadIdx.x; i < per; i += blockDim.x) {
@@ -848,8 +874,9 @@ __global__ void k_sigmoid_gate(T* __restrict__ o, long long ld_o, const T* __res
 XR_EXPORT int xr_sigmoid_gate(void* o, long long ld_o, const void* g, long long ld_g, int dtype, int n, int H, int hd, int Vd, int each,
                               cudaStream_t stream) {
     if (n < 1 || H < 1 || Vd < 1 || hd < Vd) return XR_ERR_ARG;
-    const int two = !((hd | Vd | ld_o | ld_g) & 1) && !(((uintptr_t)o | (uintptr_t)g) & 3);
-    const int work = H * Vd / (dtype == XR_BF16 && two ? 2 : 1);
+    int two = !((hd | Vd | ld_o | ld_g) & 1) && !(((uintptr_t)o | (uintptr_t)g) & 3) ? 2 : 0;
+    if (!((hd | Vd | ld_o) & 7) && !((uintptr_t)o & 15) && (!each || (!(ld_g & 7) && !((uintptr_t)g & 15)))) two = 8;
+    const int work = H * Vd / (dtype == XR_BF16 && two ? two : 1);
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
     if (dtype == XR_F32) xr_launch((k_sigmoid_gate<float>), dim3(n), dim3(threads), 0, stream, (float*)o, ld_o, (const float*)g, ld_g, H, hd, Vd, each ? 1 : 0, 0);
     else if (dtype == XR_BF16)
