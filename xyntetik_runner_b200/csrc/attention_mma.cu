@@ -56,7 +56,14 @@ struct AttnMmaArgs {
     int* status;                 // set non-zero if a bounded wait gives up
     int recv_rows;               // cluster variant: most packed rows any request of the step has (sizes what a block receives)
     const float* sink;           // [H] or null: a logit per query head that joins the softmax's denominator once (no key, no value)
+    float softcap;               // c > 0: every score becomes c tanh(score / c); 0: scores as they are
 };
+
+// c tanh(x / c) through one exponential: tanh(y) = 1 - 2 / (exp(2y) + 1), exact in the limits and within a few 1e-7 elsewhere.
+__device__ __forceinline__ float att_softcap(float x, float cap, float inv_cap) {
+    const float e = __expf(2.0f * x * inv_cap);
+    return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
 
 // What a sink adds to a row's denominator once every key has been seen: exp(sink - m), m the row's final maximum.
 __device__ __forceinline__ float att_sink_term(const float* sink, int head, float m) {
@@ -191,7 +198,7 @@ __device__ __forceinline__ const __nv_bfloat16* tile_ptr(const __nv_bfloat16* ba
 
 template <int HD, int NKT, bool LOWER_ONLY = false, bool SWZ = false>
 __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bfloat16* ks, const __nv_bfloat16* vs,
-                                          int col0, int key0, int pos_a, int pos_b, int window, float scale,
+                                          int col0, int key0, int pos_a, int pos_b, int window, float scale, float cap,
                                           float* m, float* l, float (*o)[4]) {
     const int lane = threadIdx.x & 31;
     float s[NKT][4];
@@ -212,6 +219,16 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bf
     const int t2 = (lane & 3) * 2;
     const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
     float mx_a = -INFINITY, mx_b = -INFINITY;
+    if (cap > 0.f) {
+        // capped scores: the cap is applied to the scaled score, and the scale below is then one
+        const float inv_cap = 1.0f / cap;
+#pragma unroll
+        for (int j = 0; j < NKT; j++) {
+#pragma unroll
+            for (int e = 0; e < (LOWER_ONLY ? 2 : 4); e++) s[j][e] = att_softcap(s[j][e] * scale, cap, inv_cap);
+        }
+        scale = 1.0f;
+    }
 #pragma unroll
     for (int j = 0; j < NKT; j++) {
 #pragma unroll
@@ -361,7 +378,7 @@ k_attention_rows(AttnMmaArgs a, int n_seg) {
         __syncthreads();
         if (t * ATT_TILE <= warp_hi)
             tile_step<HD, 8>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, 0, t * ATT_TILE, pos_a, pos_b,
-                             a.window, a.scale, m, l, o);
+                             a.window, a.scale, a.softcap, m, l, o);
         __syncthreads();
     }
     // rows a (lane/4) and b (+8): columns d*8 + 2*(lane%4) (+1)
@@ -442,10 +459,10 @@ k_attention_keys(AttnMmaArgs a) {
         if (kfirst <= hi && kfirst + 15 >= lo) {
             if (rows_total <= 8)
                 tile_step<HD, 2, true>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, c0, t * ATT_TILE, pos_a, pos_b,
-                                       a.window, a.scale, m, l, o);
+                                       a.window, a.scale, a.softcap, m, l, o);
             else
                 tile_step<HD, 2, false>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, c0, t * ATT_TILE, pos_a, pos_b,
-                                        a.window, a.scale, m, l, o);
+                                        a.window, a.scale, a.softcap, m, l, o);
         }
         __syncthreads();
     }
@@ -637,9 +654,9 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
         int c0 = warp * 16, kfirst = t * ATT_TILE + c0;
         if (kfirst <= hi && kfirst + 15 >= lo) {
             if (rows_total <= 8)
-                tile_step<HD, 2, true, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+                tile_step<HD, 2, true, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, a.softcap, m, l, o);
             else
-                tile_step<HD, 2, false, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+                tile_step<HD, 2, false, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, a.softcap, m, l, o);
         }
         __syncthreads();                 // everyone is done with stage `cur` before it is fetched into again
     }
@@ -986,9 +1003,9 @@ k_attention_keys_even(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs
             const int c0 = warp * 16, kfirst = t * ATT_TILE + c0;
             if (kfirst <= hi && kfirst + 15 >= lo) {
                 if (rows_total <= 8)
-                    tile_step<HD, 2, true, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+                    tile_step<HD, 2, true, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, a.softcap, m, l, o);
                 else
-                    tile_step<HD, 2, false, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+                    tile_step<HD, 2, false, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, a.softcap, m, l, o);
             }
             __syncthreads();                                       // everyone is done with stage `cur`:
             if (tid == 0 && fetched < n_mine) fetch_next();        // tile i + STAGES goes into it at once, so the ring stays full
@@ -1537,7 +1554,7 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
                                int hd, int max_pages, int page_size, int window, float scale, int max_seg_len,
                                int max_kv_len, int splits, int any_short, int any_long, const void* cache_base,
                                long long n_pages, int n_layers, int layer, int* status, int* flags, int n_flags,
-                               int uneven, long long row_tiles, const float* sink, cudaStream_t stream) {
+                               int uneven, long long row_tiles, const float* sink, float softcap, cudaStream_t stream) {
     if (n_seg < 1 || H < 1 || K < 1 || H % K != 0 || hd < 16 || hd > 128 || hd % 16 != 0 || page_size < 1 || window < 0 ||
         (q_stride % 8) != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache_k & 15) || (page_stride % 8) != 0 || (v_offset % 8) != 0)
         return XR_ERR_ARG;
@@ -1546,7 +1563,7 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
     if (any_short && splits < spans) return XR_ERR_ARG;
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  spans, 0, scale, -1, n_layers, layer, status, 16, sink};
+                  spans, 0, scale, -1, n_layers, layer, status, 16, sink, softcap};
     { long long rows = (long long)(max_seg_len < 1 ? 1 : max_seg_len) * a.G; a.recv_rows = rows < 16 ? (int)rows : 16; }
     a.span = att_choose_span(att_range(max_kv_len, window), (long long)n_seg * K);
     const long long room = (long long)splits * n_seg * K;

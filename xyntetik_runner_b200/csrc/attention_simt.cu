@@ -27,6 +27,7 @@ struct AttnArgs {
     int n, H, K, hd, max_pages, page_size, window;
     float scale;
     const float* sink;           // [H] or null: exp(sink[h]) joins the softmax's denominator once (no key, no value)
+    float softcap;               // c > 0: every score becomes c tanh(score / c); 0: scores as they are
 };
 
 #define AS_MAX_HD 256
@@ -66,6 +67,7 @@ k_attention_simt(AttnArgs a) {
             float dot = 0.f;
             for (int i = 0; i < a.hd; i++) dot = fmaf(qs[warp][i], xr_to_f32<T>(kr[i]), dot);
             s = dot * a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
         }
         float cm = xr_warp_max(s);
         float m_new = fmaxf(m, cm);
@@ -100,11 +102,12 @@ k_attention_simt(AttnArgs a) {
 XR_EXPORT int xr_attention_simt(const void* q, void* out, int dtype, const void* cache_k, const int* positions,
                                 const int* tok_seg, const int* block_tables, long long page_stride,
                                 long long v_offset, long long q_row_stride, int n, int H, int K, int hd,
-                                int max_pages, int page_size, int window, float scale, const float* sink, cudaStream_t stream) {
-    if (n < 1 || H < 1 || K < 1 || H % K != 0 || hd < 1 || hd > AS_MAX_HD || page_size < 1 || window < 0)
+                                int max_pages, int page_size, int window, float scale, const float* sink, float softcap,
+                                cudaStream_t stream) {
+    if (n < 1 || H < 1 || K < 1 || H % K != 0 || hd < 1 || hd > AS_MAX_HD || page_size < 1 || window < 0 || softcap < 0.f)
         return XR_ERR_ARG;
     AttnArgs a{q, out, cache_k, positions, tok_seg, block_tables, page_stride, v_offset, q_row_stride,
-               n, H, K, hd, max_pages, page_size, window, scale, sink};
+               n, H, K, hd, max_pages, page_size, window, scale, sink, softcap};
     long long warps = (long long)n * H;
     long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return XR_ERR_ARG;

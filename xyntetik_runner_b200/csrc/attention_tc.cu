@@ -48,6 +48,7 @@ struct AttnTcArgs {
     float scale_log2;            // scale * log2(e)
     int n_seg;
     const float* sink;           // [H] or null: exp(sink[h]) joins the denominator of every softmax of query head h once
+    float cap_over_scale, scale_over_cap;   // soft cap c > 0 on the scaled scores: c / scale and scale / c; 0: none
 };
 
 __device__ __forceinline__ uint32_t ta_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -319,6 +320,14 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             ta_ld32_nowait(tm_s, sraw);
             ta_ld32_nowait(tm_s + 32, sraw + 32);
             ta_ld_wait();
+            if (a.cap_over_scale > 0.f) {
+                // capped scores: a raw score r stands for c tanh(r scale / c) / scale from here on (tanh through one exponential)
+#pragma unroll
+                for (int i = 0; i < 64; i++) {
+                    const float e = ta_exp2(__uint_as_float(sraw[i]) * a.scale_over_cap * 2.8853900817779268f);
+                    sraw[i] = __float_as_uint(a.cap_over_scale * (1.0f - __fdividef(2.0f, e + 1.0f)));
+                }
+            }
             float v[32];
             float mx = -INFINITY;
             if (masked) {
@@ -483,7 +492,7 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
                               const int* seg_pos0, const int* block_tables, int* status, long long q_row_stride, int n,
                               int n_seg, int H, int K, int hd, int max_pages, int page_size, int window, float scale,
                               int max_seg_len, long long row_tiles, long long n_pages, int n_layers, int layer, const float* sink,
-                              cudaStream_t stream) {
+                              float softcap, cudaStream_t stream) {
     if (!xr_attention_tc_supported(H, K, hd, page_size) || n < 1 || n_seg < 1 || window < 0 || status == nullptr) return XR_ERR_ARG;
     if (((uintptr_t)q & 15) || ((uintptr_t)cache_base & 15) || (q_row_stride % 8) != 0) return XR_ERR_ARG;
     const int G = H / K;
@@ -522,7 +531,8 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     int shift = 0;
     while ((1 << shift) < page_size) shift++;
     AttnTcArgs a{(__nv_bfloat16*)out, seg_start, seg_len, seg_pos0, block_tables, status, H, K, G, max_pages, page_size, shift,
-                 window, n_layers, layer, scale * 1.4426950408889634f, n_seg, sink};
+                 window, n_layers, layer, scale * 1.4426950408889634f, n_seg, sink,
+                 softcap > 0.f ? softcap / scale : 0.f, softcap > 0.f ? scale / softcap : 0.f};
     constexpr int SMEM = 10 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
     if (!configured) {

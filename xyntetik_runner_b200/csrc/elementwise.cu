@@ -399,6 +399,8 @@ struct QkNormStoreArgs {
     // the kernel first sums a row's partials in split order, adds the bias and writes the row to `in`, all `cols` columns (columns
     // behind the values, such as gates that a later kernel reads, are finished with them).
     const float* partial; const float* bias; int splits, cols, n;
+    float mscale;                // factor on every cosine and sine
+    int norm_after;              // the unit norm is taken of the ROTATED head (with mscale other than one the order matters)
 };
 
 template <typename T>
@@ -415,6 +417,7 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     if (part * nw < a.H + a.K)                             // (a block that only finishes columns behind the heads needs no angles)
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
+            cs[half + j] *= a.mscale; cs[j] *= a.mscale;
         }
     T* kdst = nullptr;
     if (a.cache_k != nullptr) {
@@ -423,6 +426,9 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     }
     const size_t head_step = (size_t)a.page_size * a.hd;
     const float q_factor = a.q_every > 0 ? 1.0f + a.q_coef * logf((float)((pos + 1) / a.q_every) + 1.0f) : 1.0f;
+    // A turn by an angle keeps a pair's sum of squares, and cosines and sines times mscale multiply it by mscale^2: the sum of
+    // squares of the rotated head is that of the head as it is, the rotated elements weighted by mscale^2.
+    const float rot_weight = a.norm_after ? a.mscale * a.mscale : 1.0f;
     __syncthreads();
     xr_pdl_wait();
     const T* row = (const T*)a.in + (size_t)t * a.ld_in;
@@ -470,17 +476,20 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
                     const T r = xr_from_f32<T>(a.bias ? acc[k] + a.bias[c] : acc[k]);
                     wr[c] = r;
                     const float x = xr_to_f32<T>(r);
-                    mine[e] = x; ss = fmaf(x, x, ss);
+                    mine[e] = x; ss = fmaf(x * (e < a.rotary_dim ? rot_weight : 1.0f), x, ss);
                 }
             }
         } else if (pairs) {
             for (int e = 2 * lane; e < a.D; e += 64) {
                 const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(src) + e));
                 mine[e] = x.x; mine[e + 1] = x.y;
-                ss = fmaf(x.x, x.x, fmaf(x.y, x.y, ss));
+                ss = fmaf(x.x * (e < a.rotary_dim ? rot_weight : 1.0f), x.x, fmaf(x.y * (e + 1 < a.rotary_dim ? rot_weight : 1.0f), x.y, ss));
             }
         } else {
-            for (int e = lane; e < a.D; e += 32) { const float x = xr_to_f32<T>(src[e]); mine[e] = x; ss = fmaf(x, x, ss); }
+            for (int e = lane; e < a.D; e += 32) {
+                const float x = xr_to_f32<T>(src[e]);
+                mine[e] = x; ss = fmaf(x * (e < a.rotary_dim ? rot_weight : 1.0f), x, ss);
+            }
         }
         ss = xr_warp_sum(ss);
         const bool normed = w != nullptr || a.unit;
@@ -555,7 +564,11 @@ k_qk_norm_rope_store_vec(QkNormStoreArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int pos = a.positions[t];
     float* cs = qk_sm;
-    for (int j = threadIdx.x; j < half; j += blockDim.x) xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
+        cs[half + j] *= a.mscale; cs[j] *= a.mscale;
+    }
+    const float rot_weight = a.norm_after ? a.mscale * a.mscale : 1.0f;     // (see k_qk_norm_rope_store)
     __nv_bfloat16* kdst = nullptr;
     if (a.cache_k != nullptr) {
         const int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
@@ -591,6 +604,7 @@ k_qk_norm_rope_store_vec(QkNormStoreArgs a) {
         float ss = 0.f;
 #pragma unroll
         for (int k = 0; k < 8; k++) ss = fmaf(x[k], x[k], ss);
+        if (e0 < a.rotary_dim) ss *= rot_weight;              // (a lane's eight elements are all rotated or all not)
 #pragma unroll
         for (int o = SUB >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (head >= heads || e0 >= a.hd) continue;
@@ -658,16 +672,16 @@ XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, 
                                     void* cache_k, long long page_stride, long long v_offset, int n, int H, int K, int D, int Vd, int hd,
                                     int rotary_dim, int max_pages, int page_size, int adjacent_pairs, float eps, int unit_norm,
                                     float q_coef, int q_every, const float* partial, int splits, const float* bias, int cols,
-                                    cudaStream_t stream) {
+                                    float mscale, int norm_after, cudaStream_t stream) {
     if (partial != nullptr && (splits < 1 || D > 256 || cols < (H + K) * D + K * Vd || cols > ld_in)) return XR_ERR_ARG;
     if (n < 1 || H < 1 || K < 1 || D < 1 || Vd < 1 || hd < D || hd < Vd || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) ||
         page_size < 1 || (rotary_dim > 0 && freq == nullptr) || (q_w == nullptr) != (k_w == nullptr) || q_every < 0 ||
-        (unit_norm && q_w != nullptr))
+        (unit_norm && q_w != nullptr) || (norm_after && !unit_norm))
         return XR_ERR_ARG;
     const int pairs = !((D | hd | ld_in | q_ld | page_stride) & 1) && !(((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)cache_k) & 3);
     QkNormStoreArgs a{in, ld_in, q_out, q_ld, positions, tok_seg, block_tables, freq, q_w, k_w, cache_k, page_stride, v_offset,
                       H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps, pairs, unit_norm ? 1 : 0,
-                      q_coef, q_every, partial, bias, splits, cols, n};
+                      q_coef, q_every, partial, bias, splits, cols, n, mscale, norm_after ? 1 : 0};
     const size_t smem = ((size_t)rotary_dim + 8 * (size_t)D) * sizeof(float);
     if (smem > 48 * 1024) return XR_ERR_ARG;
     // bfloat16 rows of whole prompts whose sizes, strides and addresses all fall on 16-byte borders: eight elements a lane

@@ -13,7 +13,8 @@
 // Choice: one warp per token.  ids [n][top] int32, wts [n][top] float32 (in the order of descending z).
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
-k_route_topk(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int n, int E, int top) {
+k_route_topk(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int n, int E, int top,
+             const float* __restrict__ correction, int sigmoid_scores) {
     xr_pdl_launch();
     xr_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -28,7 +29,9 @@ k_route_topk(const float* __restrict__ z, int* __restrict__ ids, float* __restri
         float bv = -INFINITY;
         int be = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float v = row[e];
+            // (sigmoid scores: the choice is by score plus the expert's correction, where there is one)
+            float v = row[e];
+            if (sigmoid_scores) { v = 1.0f / (1.0f + expf(-v)); if (correction != nullptr) v += correction[e]; }
             const bool after = v < last_v || (v == last_v && e > last_e);
             if (after && (v > bv || (v == bv && e < be))) { bv = v; be = e; }
         }
@@ -39,19 +42,24 @@ k_route_topk(const float* __restrict__ z, int* __restrict__ ids, float* __restri
             if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
         }
         if (j == 0) best0 = bv;
-        const float p = expf(bv - best0);
+        // the weight: softmax over the chosen logits, or the chosen expert's score itself, without its correction
+        const float p = sigmoid_scores ? 1.0f / (1.0f + expf(-row[be < E ? be : 0])) : expf(bv - best0);
         sum += p;
         if (lane == 0) { ids[(size_t)t * top + j] = be; wts[(size_t)t * top + j] = p; }
         last_v = bv; last_e = be;
     }
     __syncwarp();
+    if (sigmoid_scores) return;
     if (lane < top) wts[(size_t)t * top + lane] /= sum;
     for (int j = 32 + lane; j < top; j += 32) wts[(size_t)t * top + j] /= sum;
 }
 
-XR_EXPORT int xr_route_topk(const float* z, int* ids, float* wts, int n, int E, int top, cudaStream_t stream) {
-    if (n < 1 || E < 1 || top < 1 || top > E) return XR_ERR_ARG;
-    xr_launch(k_route_topk, dim3((n + 3) / 4), dim3(128), 0, stream, z, ids, wts, n, E, top);
+// sigmoid_scores: scores s = sigmoid(z); the `top` largest s + correction (correction [E] float32 or null) are chosen and their
+// weights are s itself, not renormalised.  Otherwise the `top` largest z, weights their softmax.
+XR_EXPORT int xr_route_topk(const float* z, int* ids, float* wts, int n, int E, int top, const float* correction, int sigmoid_scores,
+                            cudaStream_t stream) {
+    if (n < 1 || E < 1 || top < 1 || top > E || (correction != nullptr && !sigmoid_scores)) return XR_ERR_ARG;
+    xr_launch(k_route_topk, dim3((n + 3) / 4), dim3(128), 0, stream, z, ids, wts, n, E, top, correction, sigmoid_scores ? 1 : 0);
     return xr_launch_status();
 }
 

@@ -75,6 +75,8 @@ class StepContext:
         self._memo: Dict[object, object] = {}
         self.decode_only = False       # every segment is a single token
         self.uneven = False            # the requests' lengths differ much (a hint for kernels that split work by request)
+        self.embedding_state = None    # [max_requests, ...]: what an embedding keeps per request slot (None: nothing)
+        self.stream_cast = None        # address of the stream whose rounding to the activation dtype lies in "block_normed"
 
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         # (every layer asks for the same few views: made once a step)
@@ -170,6 +172,10 @@ class Engine:
         for entry, need in self.model.state_needs:
             self.model.layers[entry].state = torch.zeros((p.max_requests,) + tuple(need.shape), dtype=need.dtype,
                                                          device=self.device)
+        # an embedding that keeps something per request (the token before a portion's first, for a table read by pairs of tokens)
+        need = getattr(plan.embedding, "state_need", lambda: None)()
+        self.embedding_state = None if need is None else torch.zeros((p.max_requests,) + tuple(need.shape), dtype=need.dtype,
+                                                                     device=self.device)
         self._bufs: Dict[tuple, torch.Tensor] = {}
         # step descriptions go through a small ring of pinned buffers; an event per buffer says when the
         # copy that read it has run, so the host never rewrites memory that a copy in flight still reads
@@ -187,7 +193,7 @@ class Engine:
         # Decode-only steps of more than 8 requests are filled up to a multiple of 8 with rows of a request that does
         # not exist (one token at position 0, keys and values in the spare page, logits dropped), so that a few graphs
         # serve every batch size.  Not with per-request state: a filler row has no slot of its own.
-        self._fill_ok = self._graph_ok and not self.model.state_needs
+        self._fill_ok = self._graph_ok and not self.model.state_needs and self.embedding_state is None
         self._graph_seen: Dict[tuple, int] = {}
         self._buf_generation = 0
         self.graph_replays = 0
@@ -240,6 +246,8 @@ class Engine:
         for lay in self.model.layers:
             if lay.state is not None:
                 lay.state[slot].zero_()
+        if self.embedding_state is not None:
+            self.embedding_state[slot].zero_()
         return slot
 
     # ---- the step ----------------------------------------------------------------
@@ -411,17 +419,21 @@ class Engine:
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         plan = self.plan
         x = ctx.buf("residual", (ctx.n, plan.width), torch.float32)
+        ctx.embedding_state = self.embedding_state
         plan.embedding.forward(ctx, ctx.token_ids, x)
         x0 = None
         if plan.keeps_embedding():
-            # the embedding's output is kept for the parts that join it to the stream again
+            # the embedding's output is kept for the parts that join it to the stream again (a copy: an embedding with a state
+            # of its own runs once a step)
             x0 = ctx.buf("embedding_out", (ctx.n, plan.width), torch.float32)
-            plan.embedding.forward(ctx, ctx.token_ids, x0)
+            x0.copy_(x)
         for lay in self.model.layers:
             entry = plan.schedule[lay.entry]
             if entry.before is not None:
                 plan.stream_parts[entry.before].forward(ctx, x, x0)
             plan.blocks[entry.layer].forward(ctx, x, lay)
+            if entry.after is not None:
+                plan.stream_parts[entry.after].forward(ctx, x, x0)
         if ctx.n_rows == 0:
             ctx.materialize(x)
             return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=self.device)

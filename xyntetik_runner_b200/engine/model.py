@@ -27,6 +27,7 @@ class ScheduleEntry:
     layer: int                         # index into ModelPlan.blocks
     cache_from: Optional[int] = None   # index of an earlier schedule entry whose keys/values this one reads
     before: Optional[int] = None       # index into ModelPlan.stream_parts: run on the residual stream right before this entry
+    after: Optional[int] = None        # the same, right behind this entry
 
 
 @dataclass
@@ -50,7 +51,7 @@ class ModelPlan:
 
     def keeps_embedding(self) -> bool:
         """Whether a step must keep the embedding's output beside the residual stream."""
-        return any(e.before is not None for e in self.schedule)
+        return any(e.before is not None or e.after is not None for e in self.schedule)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
@@ -65,8 +66,9 @@ class ModelPlan:
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
-            if e.before is not None and not (0 <= e.before < len(self.stream_parts)):
-                raise ValueError(f"schedule entry {i} names stream part {e.before}, the model has {len(self.stream_parts)}")
+            for sp in (e.before, e.after):
+                if sp is not None and not (0 <= sp < len(self.stream_parts)):
+                    raise ValueError(f"schedule entry {i} names stream part {sp}, the model has {len(self.stream_parts)}")
             if e.cache_from is not None:
                 if not (0 <= e.cache_from < i) or self.schedule[e.cache_from].cache_from is not None:
                     raise ValueError(f"schedule entry {i}: cache_from must name an earlier entry that owns a cache")
@@ -139,5 +141,5 @@ class LoadedModel:
         """Bytes of weights one step reads: every scheduled block once, the final norm and the head
         (the embedding table is read by row only)."""
         total = sum(self.plan.blocks[e.layer].weight_bytes() for e in self.plan.schedule)
-        total += sum(self.plan.stream_parts[e.before].weight_bytes() for e in self.plan.schedule if e.before is not None)
+        total += sum(self.plan.stream_parts[sp].weight_bytes() for e in self.plan.schedule for sp in (e.before, e.after) if sp is not None)
         return total + self.plan.final_norm.weight_bytes() + self.plan.head.weight_bytes()

@@ -53,18 +53,18 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_act_mul": [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
-        "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+        "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _f, _vp],
         "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
         "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
-                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _ll, _vp, _vp],
+                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _ll, _vp, _f, _vp],
         "xr_attention_mma_splits": [_i, _i, _ll],
         "xr_attention_even_launches": [],
         "xr_attention_wait_probe": [_vp, _vp, ctypes.c_uint, _vp],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
-        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp, _vp],
+        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp, _f, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
@@ -82,18 +82,27 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_heads_gather": [_vp, _ll, _i, _vp, _i, _i, _i, _i, _vp],
         "xr_heads_scatter_gate": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
         "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i,
-                                  _vp, _i, _vp, _i, _vp],
+                                  _vp, _i, _vp, _i, _f, _i, _vp],
         "xr_rmsnorm_act": [_vp, _i, _ll, _vp, _vp, _ll, _i, _i, _f, _vp],
         "xr_delta": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _vp],
+        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
-        "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
+        "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
         "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
         "xr_moe_gather": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
         "xr_gemm_tc_grouped": [_vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _ll, _ll, _i, _vp, _i, _vp, _vp],
         "xr_moe_tile_rows": [],
         "xr_moe_gemm": [_vp, _i, _ll, _vp, _i, _vp, _i, _ll, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+        "xr_embed_pair": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
+        "xr_last_token": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
+        "xr_norm_add": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+        "xr_cast_rows": [_vp, _vp, _i, _ll, _vp],
+        "xr_depth_average": [_vp, _vp, _vp, _vp, _vp, _i, _i, _ll, _vp],
+        "xr_rotate_heads": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp],
+        "xr_rglru": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                     _f, _vp],
+        "xr_decay_attention": [_vp, _ll, _i, _i, _i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -217,14 +226,15 @@ def qk_norm_rope_store(inp: torch.Tensor, q_out: torch.Tensor, positions, tok_se
                        q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], cache_k_ptr: Optional[int], page_stride: int, v_offset: int,
                        H: int, K: int, D: int, Vd: int, hd: int, rotary_dim: int, max_pages: int, page_size: int, adjacent: bool,
                        eps: float, unit_norm: bool = False, q_coef: float = 0.0, q_every: int = 0, partial: Optional[torch.Tensor] = None,
-                       splits: int = 0, bias: Optional[torch.Tensor] = None) -> None:
+                       splits: int = 0, bias: Optional[torch.Tensor] = None, mscale: float = 1.0, norm_after: bool = False) -> None:
     """inp [n, >= (H + K) D + K Vd] (rows may be strided): Q heads, K heads (D each), V heads (Vd each).  Every Q and K head is
     RMS-normed with the weight q_w / k_w (float32 [D], shared by the heads; None: no norm), its first `rotary_dim` elements rotated
     (freq: float64 [rotary_dim / 2]); Q goes to q_out [n, *] (head h at column h * hd), K and V into the token's cache rows, every
     head filled up to `hd` elements with zeros (cache_k_ptr None: nothing is stored).  `unit_norm` (with no weights): every Q
     and K head is divided by its root mean square all the same.  `q_every` > 0: the Q heads of the token at position p are
     multiplied by 1 + q_coef ln(floor((p + 1) / q_every) + 1).  `partial` (float32 [splits][n][inp.shape[1]], with `bias`): the rows are
-    still the partial sums of a product cut along K; the kernel sums them (+ bias) into `inp`, every column, before it reads them."""
+    still the partial sums of a product cut along K; the kernel sums them (+ bias) into `inp`, every column, before it reads them.
+    `mscale` multiplies every cosine and sine; `norm_after` (with `unit_norm`): the root mean square is that of the rotated head."""
     _dev(positions, tok_seg, block_tables, freq, q_w, k_w, partial, bias)
     n = inp.shape[0]
     assert partial is None or (partial.dtype == torch.float32 and splits >= 1 and partial.numel() >= splits * n * inp.shape[1])
@@ -236,7 +246,8 @@ def qk_norm_rope_store(inp: torch.Tensor, q_out: torch.Tensor, positions, tok_se
                                        positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), _ptr(q_w), _ptr(k_w),
                                        cache_k_ptr, page_stride, v_offset, n, H, K, D, Vd, hd, rotary_dim, max_pages, page_size,
                                        int(adjacent), float(eps), int(unit_norm), float(q_coef), int(q_every), _ptr(partial), int(splits),
-                                       _ptr(bias) if partial is not None else None, inp.shape[1], _stream()),
+                                       _ptr(bias) if partial is not None else None, inp.shape[1], float(mscale), int(norm_after),
+                                       _stream()),
            "qk_norm_rope_store")
     _count()
 
@@ -282,9 +293,10 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optiona
 
 def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, positions, tok_seg,
                    block_tables, page_stride: int, v_offset: int, H: int, K: int, hd: int, max_pages: int,
-                   page_size: int, window: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
+                   page_size: int, window: int, scale: float, sink: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Causal attention of every token of the step over its request's pages, float32 arithmetic.  `sink`: float32 [H];
-    exp(sink[h]) joins the denominator of head h's softmax once (it has no key and no value)."""
+    exp(sink[h]) joins the denominator of head h's softmax once (it has no key and no value).  `softcap` c > 0: every scaled
+    score s becomes c tanh(s / c)."""
     _dev(out, positions, tok_seg, block_tables, sink)
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
     n = out.shape[0]
@@ -292,7 +304,7 @@ def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_
     _check(lib().xr_attention_simt(q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache_k_ptr,
                                    positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), page_stride,
                                    v_offset, q_row_stride, n, H, K, hd, max_pages, page_size, window, float(scale),
-                                   _ptr(sink), _stream()), "attention_simt")
+                                   _ptr(sink), float(softcap), _stream()), "attention_simt")
     _count()
 
 
@@ -619,8 +631,8 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                   v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
                   n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool,
                   group: Optional[tuple] = None, uneven: bool = False, row_tiles: int = 0,
-                  sink: Optional[torch.Tensor] = None) -> None:
-    """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
+                  sink: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+    """Causal attention over the pages on tensor cores (bfloat16); `softcap` c > 0: every scaled score s becomes c tanh(s / c).  Portions with at most 16 packed rows
     (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
     and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel.
     `group` = (pointer to the cache group's array, its pages, its layers, this layer's index) lets the
@@ -643,7 +655,7 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                                   group[0] if group else None, group[1] if group else 0, group[2] if group else 1,
                                   group[3] if group else 0, ws.status.data_ptr() if group else None,
                                   ws.flags.data_ptr() if group else None, ws.flags.numel() if group else 0, int(uneven),
-                                  row_tiles, _ptr(sink), _stream()), "attention_mma")
+                                  row_tiles, _ptr(sink), float(softcap), _stream()), "attention_mma")
     _count((1 if any_long else 0) + (2 if any_short else 0))
 
 
@@ -653,7 +665,7 @@ def attention_tc_supported(dtype: torch.dtype, H: int, K: int, hd: int, page_siz
 
 def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_pos0, block_tables, group: tuple,
                  H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float, n_seg: int,
-                 max_seg_len: int, row_tiles: int = 0, sink: Optional[torch.Tensor] = None) -> None:
+                 max_seg_len: int, row_tiles: int = 0, sink: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Causal attention of the portions with more than 16 packed rows on tcgen05 (S and O in tensor memory).
     qkv: the step's fused rows (Q heads first); group = (pointer to the cache group's array, pages, layers, layer).
     row_tiles: ``long_row_tiles(lengths, H // K, 128)``, which sizes the grid exactly; 0: every portion gets the blocks
@@ -666,7 +678,7 @@ def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_p
     _check(lib().xr_attention_tc(qkv.data_ptr(), out.data_ptr(), group[0], seg_start.data_ptr(), seg_len.data_ptr(),
                                  seg_pos0.data_ptr(), block_tables.data_ptr(), status.data_ptr(), qkv.stride(0), n, n_seg,
                                  H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, row_tiles, group[1], group[2],
-                                 group[3], _ptr(sink), _stream()), "attention_tc")
+                                 group[3], _ptr(sink), float(softcap), _stream()), "attention_tc")
     _count()
 
 
@@ -865,7 +877,7 @@ def mlstm(proj: torch.Tensor, cols, gates: torch.Tensor, state: torch.Tensor, co
 
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.Tensor, y: torch.Tensor, H: int, V: int, eps: float,
-                   per_head_weight: bool = False, silu: bool = False) -> None:
+                   per_head_weight: bool = False, silu: bool = False, scale: float = 1.0) -> None:
     """y [n, H V] = o / rms(o per head) * w * act(gate[:, gate_col + h V + i]): o float32 [n, H V]; y in the activation dtype, gate
     in y's dtype or float32; w float32, V values for all heads or (`per_head_weight`) H V; act the sigmoid, or SiLU with `silu`."""
     _dev(o, w, y)
@@ -875,7 +887,7 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.
     assert w.dtype == torch.float32 and w.numel() == (H * V if per_head_weight else V) and gate.shape[1] >= gate_col + H * V
     _check(lib().xr_head_norm_gate(o.data_ptr(), gate.data_ptr() + gate_col * gate.element_size(), dtype_code(gate.dtype), gate.stride(0),
                                    w.data_ptr(), V if per_head_weight else 0, int(silu), y.data_ptr(), dtype_code(y.dtype), n, H, V,
-                                   float(eps), _stream()), "head_norm_gate")
+                                   float(eps), float(scale), _stream()), "head_norm_gate")
     _count()
 
 
@@ -911,13 +923,17 @@ def delta(proj: torch.Tensor, conv_w: torch.Tensor, gates: torch.Tensor, neg_a: 
 
 # ---------------------------------------------------------------------------
 # Routed experts (csrc/moe.cu)
-def route_topk(z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int) -> None:
-    """ids[t], wts[t]: the `top` largest of z[t] (ties: lower index) and the softmax over them alone."""
-    _dev(z, ids, wts)
+def route_topk(z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int, sigmoid_scores: bool = False,
+               correction: Optional[torch.Tensor] = None) -> None:
+    """ids[t], wts[t]: the `top` largest of z[t] (ties: lower index) and the softmax over them alone.  With `sigmoid_scores` the
+    scores are s = sigmoid(z): the `top` largest s + correction (float32 [E], optional) are chosen, and their weights are s as it is."""
+    _dev(z, ids, wts, correction)
+    assert correction is None or (sigmoid_scores and correction.dtype == torch.float32 and correction.numel() == z.shape[1])
     n, E = z.shape
     assert z.dtype == torch.float32 and ids.dtype == torch.int32 and wts.dtype == torch.float32
     assert ids.shape == (n, top) and wts.shape == (n, top)
-    _check(lib().xr_route_topk(z.data_ptr(), ids.data_ptr(), wts.data_ptr(), n, E, top, _stream()), "route_topk")
+    _check(lib().xr_route_topk(z.data_ptr(), ids.data_ptr(), wts.data_ptr(), n, E, top, _ptr(correction), int(sigmoid_scores),
+                               _stream()), "route_topk")
     _count()
 
 
@@ -996,4 +1012,111 @@ def moe_combine(d: torch.Tensor, z: torch.Tensor, wts: torch.Tensor, pair_row: t
     n, width = d.shape
     assert d.dtype == torch.float32 and z.dtype == torch.float32 and z.shape[1] == width
     _check(lib().xr_moe_combine(d.data_ptr(), z.data_ptr(), wts.data_ptr(), pair_row.data_ptr(), n, width, top, _stream()), "moe_combine")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+# Streams with other arrangements than the pre-norm block (csrc/stream.cu)
+def embed_pair(table: torch.Tensor, pairs: torch.Tensor, ids, positions, tok_seg, seg_start, seg_slot, last: torch.Tensor, x: torch.Tensor,
+               mul_prev: int, mul_cur: int, feed: Optional[torch.Tensor] = None) -> None:
+    """x[t] = table[id_t] + pairs[(prev_t * mul_prev + id_t * mul_cur) mod buckets], buckets = pairs' rows - 1; a request's first
+    token reads pairs' last row; prev_t of a portion's first token is last[slot] (int32 [slots], see ``last_token``)."""
+    _dev(table, pairs, ids, positions, tok_seg, seg_start, seg_slot, last, x, feed)
+    n, d = x.shape
+    assert table.dtype == pairs.dtype and table.shape[1] == d and pairs.shape[1] == d and pairs.shape[0] >= 2
+    assert x.dtype == torch.float32 and last.dtype == torch.int32 and ids.dtype == torch.int32
+    _check(lib().xr_embed_pair(table.data_ptr(), pairs.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), _ptr(feed),
+                               0 if feed is None else feed.numel(), positions.data_ptr(), tok_seg.data_ptr(), seg_start.data_ptr(),
+                               seg_slot.data_ptr(), last.data_ptr(), x.data_ptr(), n, d, table.shape[0], pairs.shape[0] - 1, int(mul_prev),
+                               int(mul_cur), _stream()), "embed_pair")
+    _count()
+
+
+def last_token(ids, seg_start, seg_len, seg_slot, last: torch.Tensor, n_seg: int, vocab: int, feed: Optional[torch.Tensor] = None) -> None:
+    """last[slot of portion s] = the portion's last token."""
+    _dev(ids, seg_start, seg_len, seg_slot, last, feed)
+    _check(lib().xr_last_token(ids.data_ptr(), _ptr(feed), 0 if feed is None else feed.numel(), seg_start.data_ptr(), seg_len.data_ptr(),
+                               seg_slot.data_ptr(), last.data_ptr(), n_seg, vocab, _stream()), "last_token")
+    _count()
+
+
+def norm_add(d: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, cast: Optional[torch.Tensor] = None, clear: bool = False) -> None:
+    """x[t] += d[t] / sqrt(mean(d[t]^2) + eps) * gain (one float32 number on the device); `cast` also receives the new x in its
+    dtype; `clear` zeroes d behind the read."""
+    _dev(d, x, gain, cast)
+    n, w = x.shape
+    assert d.shape == (n, w) and d.dtype == torch.float32 and x.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == 1
+    assert cast is None or cast.shape == (n, w)
+    _check(lib().xr_norm_add(d.data_ptr(), x.data_ptr(), gain.data_ptr(), _ptr(cast), 0 if cast is None else dtype_code(cast.dtype), n, w,
+                             float(eps), int(clear), _stream()), "norm_add")
+    _count()
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x in out's dtype (x float32)."""
+    _dev(x, out)
+    assert x.dtype == torch.float32 and out.numel() == x.numel()
+    _check(lib().xr_cast_rows(x.data_ptr(), out.data_ptr(), dtype_code(out.dtype), x.numel(), _stream()), "cast_rows")
+    _count()
+
+
+def depth_average(x: torch.Tensor, x0: torch.Tensor, hist: torch.Tensor, w: torch.Tensor, k: int, cast: Optional[torch.Tensor] = None) -> None:
+    """hist[k-1] <- x;  x <- w[0] x0 + sum_(j=1..k-1) w[j] hist[j-1] + w[k] x (the old x); float32; `cast` also receives the new x."""
+    _dev(x, x0, hist, w, cast)
+    assert x.dtype == torch.float32 and x0.shape == x.shape and hist.dtype == torch.float32 and hist.shape[0] >= k and hist[0].numel() == x.numel()
+    assert w.dtype == torch.float32 and w.numel() == k + 1
+    _check(lib().xr_depth_average(x.data_ptr(), x0.data_ptr(), hist.data_ptr(), w.data_ptr(), _ptr(cast),
+                                  0 if cast is None else dtype_code(cast.dtype), k, x.numel(), _stream()), "depth_average")
+    _count()
+
+
+def rotate_heads(rows: torch.Tensor, col0: int, heads: int, head_stride: int, dims: int, live: int, adjacent: bool, freq: torch.Tensor,
+                 positions, sign: float = 1.0, scale: float = 1.0) -> None:
+    """In place, for every row t and head h: the first `dims` elements at column col0 + h * head_stride are turned in pairs by
+    sign * position_t * freq[m] (freq float64), then the head's first `live` elements are multiplied by `scale`."""
+    _dev(freq, positions)
+    assert rows.stride(1) == 1 and rows.is_cuda and rows.shape[1] >= col0 + (heads - 1) * head_stride + live
+    assert freq.dtype == torch.float64 and freq.numel() >= dims // 2
+    _check(lib().xr_rotate_heads(rows.data_ptr(), dtype_code(rows.dtype), rows.stride(0), col0, heads, head_stride, dims, live, int(adjacent),
+                                 freq.data_ptr(), positions.data_ptr(), float(sign), float(scale), rows.shape[0], _stream()), "rotate_heads")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+# Linear recurrences (csrc/recurrent.cu)
+def rglru_state_floats(R: int, taps: int) -> int:
+    """float32 values per request slot: S [R], then the last taps - 1 inputs of the convolution [taps - 1][R]."""
+    return R * taps
+
+
+def rglru(proj: torch.Tensor, conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state: torch.Tensor, tok_seg, seg_start, seg_len, seg_slot,
+          a_s: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor, n_seg: int, R: int, B: int, taps: int, c: float) -> None:
+    """The real-gated linear recurrent unit over the step's tokens, request by request, from and into `state`.  proj [n, >= 2R]
+    float32 (rows may be strided): the gated branch's pre-activations in columns [0, R), the convolution's inputs in [R, 2R).
+    out [n, R] = S * gelu_tanh(gated branch).  See csrc/recurrent.cu for the other arguments."""
+    _dev(conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state, tok_seg, seg_start, seg_len, seg_slot, a_s, b_s, out)
+    n = proj.shape[0]
+    Bs = R // B
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= 2 * R and out.shape == (n, R)
+    assert all(t.dtype == torch.float32 for t in (conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state, a_s, b_s))
+    assert conv_w.shape == (R, taps) and wa_t.shape == (B, Bs, Bs) and wi_t.shape == (B, Bs, Bs) and a_s.numel() >= n * R and b_s.numel() >= n * R
+    assert state.dim() == 2 and state.shape[1] >= rglru_state_floats(R, taps)
+    _check(lib().xr_rglru(proj.data_ptr(), proj.stride(0), 0, R, conv_w.data_ptr(), conv_b.data_ptr(), wa_t.data_ptr(), wi_t.data_ptr(),
+                          ba.data_ptr(), bi.data_ptr(), lam.data_ptr(), state.data_ptr(), state.stride(0), tok_seg.data_ptr(),
+                          seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), out.data_ptr(),
+                          dtype_code(out.dtype), n, n_seg, R, B, taps, float(c), _stream()), "rglru")
+    _count(2)
+
+
+def decay_attention(proj: torch.Tensor, cols, decay: torch.Tensor, state: torch.Tensor, seg_start, seg_len, seg_slot, o: torch.Tensor,
+                    n_seg: int, H: int, D: int, V: int) -> None:
+    """Linear attention with a constant decay per head: S <- decay_h S + k v^T, o = S^T q, with q, k, v = silu of proj's columns at
+    cols = (q, k, v); proj float32 [n, *], state float32 [slots, >= H D V], o float32 [n, H V]."""
+    _dev(decay, state, seg_start, seg_len, seg_slot, o)
+    n = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and o.shape == (n, H * V) and o.dtype == torch.float32
+    assert decay.dtype == torch.float32 and decay.numel() == H and state.dtype == torch.float32 and state.shape[1] >= H * D * V
+    _check(lib().xr_decay_attention(proj.data_ptr(), proj.stride(0), cols[0], cols[1], cols[2], decay.data_ptr(), state.data_ptr(),
+                                    state.stride(0), seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), o.data_ptr(), n_seg, H, D, V,
+                                    _stream()), "decay_attention")
     _count()

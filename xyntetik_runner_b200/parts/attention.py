@@ -22,6 +22,13 @@ and has no key and no value (every attention kernel adds exp(sink - m) to a row'
 the heads' outputs are multiplied by sigmoid(W_g h) before the output product, "each" element by its own gate (W_g of
 H x Vd rows) or "head" by head (W_g of H rows); W_g's rows ride in the fused projection.  Biases (`bias`, with
 `bias_suffix`; `out_bias` for the output product's) combine with all of these.
+
+`norm_after_rotation` (with `qk_norm="unit"`): the heads are rotated first and divided by their root mean square afterwards, which
+differs from the other order when the position encoding scales its cosines and sines.  `value_rotation=(base, pairing)`: the
+value of position j is turned by j over all its Vd elements (pair m by j base^(-2m/Vd)) before it is cached, and every head's sum
+at position i is turned back by -i, so that what a query reads of a value depends on their distance.  `softcap` c: every scaled
+score s becomes c tanh(s / c).  `sink=0.0` (a number instead of a tensor's name): a sink of that logit for every head, which adds
+exp(sink) to every softmax's denominator.  `out_scale` multiplies the heads' outputs before the output product.
 """
 from __future__ import annotations
 
@@ -54,7 +61,9 @@ class GQAAttention(Mixer):
                  q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj", weight_suffix: str = ".weight",
                  value_dim: Optional[int] = None, qk_norm=False, norm_eps: float = 1e-6,
                  q_norm: str = "q.norm", k_norm: str = "k.norm", bias_suffix: str = ".bias", out_bias: Optional[bool] = None,
-                 q_temp: Optional[tuple] = None, sink: Optional[str] = None, gate: Optional[str] = None, g: str = "g"):
+                 q_temp: Optional[tuple] = None, sink=None, gate: Optional[str] = None, g: str = "g",
+                 norm_after_rotation: bool = False, value_rotation: Optional[tuple] = None, softcap: Optional[float] = None,
+                 out_scale: float = 1.0):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         if qk_norm not in (False, True, "unit"):
@@ -63,10 +72,14 @@ class GQAAttention(Mixer):
             raise ValueError(f"{prefix}: gate is None, 'head' or 'each'")
         if q_temp is not None and (len(q_temp) != 2 or int(q_temp[1]) < 1):
             raise ValueError(f"{prefix}: q_temp is (coefficient, positions per step >= 1)")
+        if norm_after_rotation and qk_norm != "unit":
+            raise ValueError(f"{prefix}: norm_after_rotation goes with qk_norm='unit'")
+        if value_rotation is not None and (len(value_rotation) != 2 or value_rotation[1] not in ("half", "adjacent")):
+            raise ValueError(f"{prefix}: value_rotation is (base, 'half' or 'adjacent')")
         self.D = head_dim                                      # query/key elements per head
         self.Vd = head_dim if value_dim is None else value_dim  # value elements per head
         # the general path: a norm per head, or values of another size than keys
-        self.general = bool(qk_norm) or self.Vd != self.D or q_temp is not None or gate is not None
+        self.general = bool(qk_norm) or self.Vd != self.D or q_temp is not None or gate is not None or value_rotation is not None
         # head size of the cache and of the attention kernels
         hd = -(-max(self.D, self.Vd) // 16) * 16 if self.general else head_dim
         if not (1 <= hd <= 256):
@@ -80,7 +93,14 @@ class GQAAttention(Mixer):
         self.norm_names = (prefix + q_norm, prefix + k_norm)
         self.bias_suffix, self.out_bias = bias_suffix, bool(bias) if out_bias is None else bool(out_bias)
         self.q_temp = None if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
-        self.sink_name = None if sink is None else prefix + sink
+        self.sink_name = prefix + sink if isinstance(sink, str) else None
+        self.sink_value = float(sink) if sink is not None and not isinstance(sink, str) else None
+        self.norm_after, self.value_rotation = bool(norm_after_rotation), value_rotation
+        self.softcap = float(softcap) if softcap else 0.0
+        self.out_scale = float(out_scale)
+        if value_rotation is not None and self.Vd % 2:
+            raise ValueError(f"{prefix}: rotated values need an even value size")
+        self.vfreq64 = None
         self.gate, self.gate_name = gate, prefix + g
         self.gate_cols = 0 if gate is None else (heads * self.Vd if gate == "each" else heads)
         self.sink = None
@@ -128,6 +148,11 @@ class GQAAttention(Mixer):
             obias = tensors[o + self.bias_suffix]
         if self.sink_name is not None:
             self.sink = tensors[self.sink_name].to(torch.float32).contiguous()
+        elif self.sink_value is not None:
+            self.sink = torch.full((self.H,), self.sink_value, dtype=torch.float32, device=rt.device)
+        if self.value_rotation is not None:
+            vf = np.power(float(self.value_rotation[0]), -2.0 * np.arange(self.Vd // 2, dtype=np.float64) / float(self.Vd))
+            self.vfreq64 = torch.from_numpy(vf).to(rt.device)
         self.qkv = Linear(torch.cat(ws, dim=0), bias).prepare(rt)
         del ws
         wo = tensors[o + sfx]
@@ -152,8 +177,6 @@ class GQAAttention(Mixer):
         self.rot = (0, None, False, 1.0) if rot is None or rot.rotary_dim == 0 else \
             (rot.rotary_dim, rot.inv_freq, rot.pairing == "adjacent", rot.mscale)
         if self.general and self.rot[0]:
-            if self.rot[3] != 1.0:
-                raise ValueError(f"{self.prefix}: scaled cosines and sines are not combined with qk_norm or value_dim")
             f64 = getattr(self.position, "inv_freq64_host", None)
             f64 = rot.inv_freq.double().cpu().numpy() if f64 is None else f64
             self.freq64 = torch.from_numpy(np.ascontiguousarray(f64, dtype=np.float64)).to(rt.device)
@@ -184,14 +207,17 @@ class GQAAttention(Mixer):
             gate_at = (self.H + self.K) * self.D + self.K * self.Vd
             cols = gate_at + self.gate_cols
             proj = ctx.buf("attn_proj", (n, -(-cols // 8) * 8), ctx.act_dtype)[:, :cols]
-            # (a product that was cut along K leaves its partial sums to the same kernel)
-            pend = self.qkv.forward(h, proj, defer=True)
+            # (a product that was cut along K leaves its partial sums to the same kernel; not where the values are turned first)
+            pend = self.qkv.forward(h, proj, defer=self.value_rotation is None)
+            if self.value_rotation is not None:
+                kernels.rotate_heads(proj, (self.H + self.K) * self.D, self.K, self.Vd, self.Vd, self.Vd, self.value_rotation[1] == "adjacent",
+                                     self.vfreq64, ctx.positions)
             coef, every = self.q_temp if self.q_temp is not None else (0.0, 0)
             kernels.qk_norm_rope_store(proj, qkv, ctx.positions, ctx.tok_seg, bt, self.freq64, self.q_norm_w, self.k_norm_w, store_ptr,
                                        page_stride, v_offset, self.H, self.K, self.D, self.Vd, self.hd, rot_dim, ctx.max_pages,
                                        ctx.page_size, adjacent, self.norm_eps, self.unit_norm, coef, every,
                                        partial=None if pend is None else pend.partial, splits=0 if pend is None else pend.splits,
-                                       bias=None if pend is None else pend.bias)
+                                       bias=None if pend is None else pend.bias, mscale=mscale, norm_after=self.norm_after)
             if pend is not None:
                 pend.release()
         else:
@@ -223,7 +249,7 @@ class GQAAttention(Mixer):
                 # prompt portions: S = Q K^T and O += P V on tcgen05
                 kernels.attention_tc(qkv, o, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, ctx.cache_group(lay), self.H,
                                      self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, ctx.n_seg,
-                                     longest, row_tiles=tiles_tc, sink=self.sink)
+                                     longest, row_tiles=tiles_tc, sink=self.sink, softcap=self.softcap)
                 counters["tcgen05"] += 1
                 any_long = False
             if any_short or any_long:
@@ -231,15 +257,27 @@ class GQAAttention(Mixer):
                                       page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
                                       self.window or 0, self.scale, ctx.n_seg, longest, ctx.max_kv_len, splits,
                                       any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None, uneven=ctx.uneven,
-                                      row_tiles=tiles_rows, sink=self.sink)
+                                      row_tiles=tiles_rows, sink=self.sink, softcap=self.softcap)
                 counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
-                                   self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, sink=self.sink)
+                                   self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, sink=self.sink, softcap=self.softcap)
             counters["simt"] += 1
         if self.gate is not None:
             kernels.sigmoid_gate(o, proj[:, gate_at:gate_at + self.gate_cols], self.H, self.hd, self.Vd, self.gate == "each")
+        if self.value_rotation is not None:
+            # the sums are turned back by their own position (and scaled in the same pass)
+            kernels.rotate_heads(o, 0, self.H, self.hd, self.Vd, self.Vd, self.value_rotation[1] == "adjacent", self.vfreq64, ctx.positions,
+                                 sign=-1.0, scale=self.out_scale)
+        elif self.out_scale != 1.0:
+            kernels.rotate_heads(o, 0, self.H, self.hd, 0, self.hd, False, self.freq64 if self.freq64 is not None else self._no_freq(o),
+                                 ctx.positions, scale=self.out_scale)
         ctx.set_pending(x, self.out.forward(o, x, accumulate=True, defer=True))
+
+    def _no_freq(self, like):
+        if getattr(self, "_empty_freq", None) is None:
+            self._empty_freq = torch.zeros(1, dtype=torch.float64, device=like.device)
+        return self._empty_freq
 
 
 register_mixer("gqa_attention", GQAAttention)

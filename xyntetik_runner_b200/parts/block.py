@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from .base import Block, FeedForward, Mixer, Norm, register_block
-from .norm import RMSNorm
+from .norm import RMSNorm, ScalarRMSNorm
 
 
 class PreNormBlock(Block):
@@ -116,3 +116,61 @@ class ParallelBlock(Block):
 
 
 register_block("parallel", ParallelBlock)
+
+
+class OutputNormBlock(Block):
+    """Norms on the sublayers' OUTPUTS: x += norm1(mixer(x)), then x += norm2(ff(x)).  The sublayers read the stream itself (in the
+    activation dtype); each adds into a float32 sum of its own, whose norm (a ``ScalarRMSNorm``: one gain for all coordinates) is
+    added into x in one pass, in float32.  The same pass writes the new x in the activation dtype for the sublayer that follows;
+    a layer reads its input from ``ctx.stream_cast`` where the part ahead of it left one (see ``parts.stream.DepthAverage``)."""
+
+    def __init__(self, mixer_norm: ScalarRMSNorm, mixer: Mixer, ff_norm: ScalarRMSNorm = None, feed_forward: FeedForward = None):
+        if (ff_norm is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
+    def tensors(self):
+        out = {}
+        for p in self.parts():
+            out.update(p.tensors())
+        return out
+
+    def bind(self, tensors, rt):
+        for p in self.parts():
+            p.bind(tensors, rt)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self.parts())
+
+    def forward(self, ctx, x, lay):
+        from .. import kernels
+        n, width = x.shape
+        ctx.materialize(x)
+        narrow = ctx.act_dtype != torch.float32
+        # what the sublayers read: the stream itself in the true 32-bit path, its rounding otherwise
+        h = x
+        if narrow:
+            h = ctx.buf("block_normed", (n, width), ctx.act_dtype)
+            if getattr(ctx, "stream_cast", None) != x.data_ptr():
+                kernels.cast_rows(x, h)
+        ctx.stream_cast = None
+        d = ctx.buf("block_sum", (n, width), torch.float32)
+        d.zero_()
+        self.mixer.forward(ctx, h, d, lay)
+        ctx.materialize(d)
+        last = self.feed_forward is None
+        kernels.norm_add(d, x, self.mixer_norm.gain, self.mixer_norm.eps, cast=h if narrow and not last else None, clear=not last)
+        if not last:
+            self.feed_forward.forward(ctx, h, d)
+            ctx.materialize(d)
+            kernels.norm_add(d, x, self.ff_norm.gain, self.ff_norm.eps)
+
+
+register_block("output_norm", OutputNormBlock)

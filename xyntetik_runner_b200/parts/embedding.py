@@ -32,6 +32,42 @@ class Embedding(Part):
         kernels.embed(self.table, ids, x, getattr(ctx, "token_feed", None), self.scale)
 
 
+class PairEmbedding(Embedding):
+    """x[t] = E[id_t] + P[row_t]: a second table read by a hash of (previous token, token),
+    row_t = (prev_t * mul_prev + id_t * mul_cur) mod buckets; the first token of a request reads row `buckets`, the table's last.
+    The token before a portion's first is part of the request's state: one int32 per request slot, which the engine keeps
+    (``state_need``) and hands over as ``ctx.embedding_state``; it is set behind every step."""
+
+    def __init__(self, vocab: int, width: int, name: str, pairs_name: str, buckets: int, mul_prev: int, mul_cur: int):
+        super().__init__(vocab, width, name)
+        if buckets < 1:
+            raise ValueError("the pair table needs at least one bucket")
+        self.pairs_name, self.buckets, self.mul_prev, self.mul_cur = pairs_name, int(buckets), int(mul_prev), int(mul_cur)
+        self.pairs = None
+
+    def state_need(self):
+        from .base import StateNeed
+        return StateNeed((1,), torch.int32)
+
+    def tensors(self):
+        t = super().tensors()
+        t[self.pairs_name] = TensorSpec((self.buckets + 1, self.width), kind="matrix")
+        return t
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.pairs = tensors[self.pairs_name]
+        if self.pairs.dtype != self.table.dtype:
+            self.table, self.pairs = self.table.to(torch.float32), self.pairs.to(torch.float32)
+
+    def forward(self, ctx, ids: torch.Tensor, x: torch.Tensor) -> None:
+        feed = getattr(ctx, "token_feed", None)
+        last = ctx.embedding_state
+        kernels.embed_pair(self.table, self.pairs, ids, ctx.positions, ctx.tok_seg, ctx.seg_start, ctx.seg_slot, last, x,
+                           self.mul_prev, self.mul_cur, feed)
+        kernels.last_token(ids, ctx.seg_start, ctx.seg_len, ctx.seg_slot, last, ctx.n_seg, self.vocab, feed)
+
+
 class Head(Part):
     graph_safe = True
     """`tied_to` set: no tensor of its own, multiplies by the embedding table."""

@@ -3,6 +3,8 @@
     z = W_router h (float32);  the `top` experts with the largest z;  weights = softmax over the chosen z alone
     out = sum_j weight_j * expert_{e_j}(h)  (+ shared(h))
     expert(h) = W_down gate_act(W_gate h, W_up h), no biases
+With ``scoring="sigmoid"`` the scores are s = sigmoid(z); the `top` largest s + correction are chosen (`correction`: a tensor of
+one number per expert, or None) and the weights are the chosen experts' s, not renormalised.
 The activation is one of ``kernels.ACTIVATIONS`` (with its `limit` where it has one).  Experts' matrices are kept as
 [experts, rows, columns] arrays; the (token, choice) pairs are put in the order of their experts on the device and every
 expert multiplies the rows that chose it (csrc/moe.cu), so no step waits for the host.
@@ -26,18 +28,26 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, width: int, experts: int, top: int, inner: int, prefix: str, activation: str = "silu",
                  limit: float = 0.0, shared: Optional[GatedFeedForward] = None, router: str = "router",
-                 expert: str = "e{}.", gate: str = "gate", up: str = "up", down: str = "down"):
+                 expert: str = "e{}.", gate: str = "gate", up: str = "up", down: str = "down", scoring: str = "softmax",
+                 correction: Optional[str] = None):
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"{prefix}: scoring is 'softmax' (over the chosen logits) or 'sigmoid'")
+        if correction is not None and scoring != "sigmoid":
+            raise ValueError(f"{prefix}: a correction of the choice goes with sigmoid scores")
         if not (1 <= top <= experts):
             raise ValueError(f"{prefix}: top {top} of {experts} experts")
         self.width, self.E, self.top, self.inner, self.prefix = width, experts, top, inner, prefix
         self.act, self.limit, self.shared = _act_id(activation), float(limit), shared
         self.router_name = prefix + router
+        self.sigmoid, self.correction_name, self.correction = scoring == "sigmoid", None if correction is None else prefix + correction, None
         self.expert_names = [tuple(prefix + expert.format(e) + s for s in (gate, up, down)) for e in range(experts)]
         self.router = self.w_gate_up = self.w_down = None
         self.tensor_cores, self._nbytes = False, 0
 
     def tensors(self):
         t = {self.router_name: TensorSpec((self.E, self.width))}
+        if self.correction_name is not None:
+            t[self.correction_name] = TensorSpec((self.E,), "vector", "zeros")
         for g, u, d in self.expert_names:
             t[g] = TensorSpec((self.inner, self.width))
             t[u] = TensorSpec((self.inner, self.width))
@@ -48,6 +58,8 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors, rt):
         self.router = Linear(tensors[self.router_name]).prepare(rt)
+        if self.correction_name is not None:
+            self.correction = tensors[self.correction_name].to(torch.float32).contiguous()
         ws = [tensors.pop(n) for names in self.expert_names for n in names]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.to(torch.float32) for w in ws]
@@ -84,7 +96,7 @@ class RoutedExperts(FeedForward):
         self.router.forward(h, z)
         ids = ctx.buf("moe_ids", (n, top), torch.int32)
         wts = ctx.buf("moe_weights", (n, top), torch.float32)
-        kernels.route_topk(z, ids, wts, top)
+        kernels.route_topk(z, ids, wts, top, self.sigmoid, self.correction)
         align = self._row_tile(pairs, E) if self.tensor_cores else kernels.moe_tile_rows()
         max_tiles = kernels.moe_max_tiles(pairs, E, align)
         rows = max_tiles * align

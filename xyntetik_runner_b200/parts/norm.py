@@ -45,4 +45,18 @@ class RMSNorm(Norm):
         kernels.rmsnorm(x, self.weight, out, self.eps, rows, w2, out2)
 
 
+class ScalarRMSNorm(RMSNorm):
+    """RMSNorm whose weight is ONE number for all coordinates: y = x * rsqrt(mean(x^2) + eps) * g.  The number is spread over the
+    width when the part binds, and the kernels are the RMSNorm's."""
+
+    def tensors(self):
+        return {self.name: TensorSpec((), kind="vector", init="ones_jitter")}
+
+    def bind(self, tensors, rt):
+        g = tensors[self.name].to(torch.float32).reshape(1)
+        self.gain = g.contiguous()
+        self.weight = g.expand(self.width).contiguous()
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("scalar_rmsnorm", ScalarRMSNorm)

@@ -74,6 +74,40 @@ class Rope(PositionEncoding):
         return Rotary(self.rotary_dim, self.inv_freq if self.rotary_dim else None, self.pairing, self.mscale)
 
 
+class YarnRope(PositionEncoding):
+    """Rotation with frequencies interpolated by wavelength ("YaRN") and cosines and sines scaled for it.
+
+    With f_i = base^(-2i/dims) and where(t) = dims ln(original / (2 pi t)) / (2 ln base), the pair index whose wavelength fits
+    `original` positions t times:  lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1),
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency_i = f_i / factor * ramp_i + f_i (1 - ramp_i); every cosine
+    and sine is multiplied by 0.1 ln(factor) + 1.  Without `factor` the frequencies are f_i and the multiplier is one."""
+
+    def __init__(self, head_dim: int, base: float, rotary_dim: int, factor: Optional[float] = None, original: float = 0.0,
+                 fast: float = 32.0, slow: float = 1.0, pairing: str = "half"):
+        if rotary_dim % 2 or rotary_dim > head_dim or rotary_dim < 0:
+            raise ValueError("rotary_dim must be even and at most head_dim")
+        self.head_dim, self.rotary_dim, self.pairing = head_dim, rotary_dim, pairing
+        half = rotary_dim // 2
+        i = np.arange(half, dtype=np.float64)
+        f = np.power(float(base), -2.0 * i / float(rotary_dim)) if half else i
+        self.mscale = 1.0
+        if factor is not None and half:
+            where = lambda turns: rotary_dim * math.log(float(original) / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+            lo, hi = max(math.floor(where(fast)), 0), min(math.ceil(where(slow)), rotary_dim - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / float(factor) * ramp + f * (1.0 - ramp)
+            self.mscale = 0.1 * math.log(float(factor)) + 1.0
+        self.inv_freq64_host = f
+        self.inv_freq_host = f.astype(np.float32)
+        self.inv_freq = None
+
+    def prepare(self, rt):
+        self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(rt.device)
+
+    def rotary(self):
+        return Rotary(self.rotary_dim, self.inv_freq if self.rotary_dim else None, self.pairing, self.mscale)
+
+
 class NoPosition(PositionEncoding):
     """No position signal of its own (order comes from the causal mask alone)."""
 
@@ -82,4 +116,5 @@ class NoPosition(PositionEncoding):
 
 
 register_position("rope", Rope)
+register_position("yarn", YarnRope)
 register_position("none", NoPosition)

@@ -6,6 +6,9 @@ weights feeds the embedding back in this way at the start of every pass.
 
 ``StreamStep``: x <- x (+ x0) + v, v one row of a table [passes, width]: such a model may instead add the embedding's
 output (from the second pass on) and a vector of the pass, in float32.
+
+``DepthAverage``: x <- sum_(j=0..k) w[j] X_j behind layer k - 1, where X_0 is the embedding's output and X_j what layer j - 1 left
+BEFORE its own average: every layer reads a learned mixture of all the streams so far.
 """
 from __future__ import annotations
 
@@ -65,3 +68,35 @@ class StreamStep(Part):
     def forward(self, ctx, x: torch.Tensor, x0: torch.Tensor) -> None:
         ctx.materialize(x)
         kernels.stream_step(x, x0 if self.add_embedding else None, self.vector)
+
+
+class DepthAverage(Part):
+    """Behind the k-th layer run (k from 1): keep x as X_k and set x <- w[0] X_0 + ... + w[k] X_k, in float32.  The streams X_1 ..
+    X_(depth) of a step live in one buffer of the step; X_0 is the embedding's output, which the engine keeps.  In the serving
+    precision the new x is also left in the activation dtype for the layer that follows (``ctx.stream_cast``)."""
+    graph_safe = True
+
+    def __init__(self, width: int, name: str, k: int, depth: int, cast: bool = True):
+        if not (1 <= k <= depth):
+            raise ValueError(f"{name}: layer run {k} of {depth}")
+        self.width, self.name, self.k, self.depth, self.cast = width, name, k, depth, bool(cast)
+        self.weights = None
+
+    def tensors(self):
+        return {self.name: TensorSpec((self.k + 1,), kind="vector", init="ones_jitter")}
+
+    def bind(self, tensors, rt):
+        self.weights = tensors[self.name].to(torch.float32).contiguous()
+
+    def weight_bytes(self):
+        return (self.k + 1) * 4
+
+    def forward(self, ctx, x: torch.Tensor, x0: torch.Tensor) -> None:
+        ctx.materialize(x)
+        n = x.shape[0]
+        hist = ctx.buf("depth_streams", (self.depth, n, self.width), torch.float32)
+        h = None
+        if self.cast and ctx.act_dtype != torch.float32:
+            h = ctx.buf("block_normed", (n, self.width), ctx.act_dtype)
+        kernels.depth_average(x, x0, hist, self.weights, self.k, cast=h)
+        ctx.stream_cast = x.data_ptr() if h is not None else None
