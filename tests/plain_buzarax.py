@@ -126,7 +126,7 @@ def causal_conv(z: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor) -> torc
     """z [T, C], taps [C, K]: out[t] = bias + sum_j taps[:, K-1-j] z[t-j], zeros before the start."""
     T, K = z.shape[0], taps.shape[1]
     out = bias.expand(T, -1).clone()
-    for j in range(K):
+    for j in range(min(K, T)):
         out[j:] += taps[:, K - 1 - j] * z[:T - j] if j else taps[:, K - 1] * z
     return out
 
@@ -182,14 +182,19 @@ def _sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
+def sublayer_input(x: torch.Tensor) -> torch.Tensor:
+    """What a sublayer reads of the stream: the stream itself.  (A test replaces this to see what a rounding here does.)"""
+    return x
+
+
 def layer(x: torch.Tensor, tensors: Dict[str, torch.Tensor], i: int, lay: dict, eps: float) -> torch.Tensor:
     """x + norm1(mixer(x)), then the same with the feed-forward: the norms act on what the sublayers give."""
     mix = {"rglru": gated_recurrence, "parallel": parallel_mixer}[lay["type"]]
-    x = x + scalar_norm(mix(x, _sub(tensors, f"l{i}.mix."), lay["mixer"], eps), tensors[f"l{i}.norm1"], eps)
+    x = x + scalar_norm(mix(sublayer_input(x), _sub(tensors, f"l{i}.mix."), lay["mixer"], eps), tensors[f"l{i}.norm1"], eps)
     f = lay.get("mlp")
     if f:
         ff = dense_ff if f["kind"] == "dense" else routed_ff
-        x = x + scalar_norm(ff(x, _sub(tensors, f"l{i}.mlp."), f), tensors[f"l{i}.norm2"], eps)
+        x = x + scalar_norm(ff(sublayer_input(x), _sub(tensors, f"l{i}.mlp."), f), tensors[f"l{i}.norm2"], eps)
     return x
 
 

@@ -106,7 +106,7 @@ def run_plain(args) -> int:
     from .config.base import read_config_json
     from .config.registry import architecture_name
     arch_name = architecture_name(read_config_json(args.model))
-    if arch_name in ("Turudra", "Besolix", "Pitolix"):
+    if arch_name in ("Turudra", "Besolix", "Pitolix", "Buzarax"):
         # the plain implementations of these architectures take the configuration and the tensors as they are stored
         import importlib
         import numpy as np
