@@ -9,6 +9,7 @@
     python bench.py --designs w2048 [--batch B] [--context C]  # a Turudra model beside a Llama of equal size (xyntetik_runner_b200/measure_designs.py)
     python bench.py --designs besolix-w2048                    # a Besolix model beside a Llama of equal size
     python bench.py --designs pitolix-w2048                    # a Pitolix model beside a Llama of equal size
+    python bench.py --designs buzarax-w2048                    # a Buzarax model beside a Llama of equal size
     python bench.py --kernel gemm --tokens 8 --rows 4096 --k 14336 --epilogue add [--plain]     # one kernel alone (for a profiler)
     XRB200_TRACE=1 python bench.py --timeline --batch 8 --layers 8                              # one layer of a decode step, kernel by kernel
 
@@ -336,8 +337,8 @@ def main() -> int:
     ap.add_argument("--workload", choices=["decode", "mixed"], default="decode",
                     help="mixed: many requests with prompts of mixed length through Runner.generate (default shape llama-3.2-1b)")
     ap.add_argument("--step-log", default=None, metavar="FILE", help="with --workload mixed: write one line per step to FILE")
-    ap.add_argument("--designs", choices=["w1024", "w2048", "besolix-w1024", "besolix-w2048", "pitolix-w1024", "pitolix-w2048"], default=None,
-                    help="instead of the benchmark: prefill and decode of a Turudra (w...), a Besolix (besolix-w...) or a Pitolix (pitolix-w...) model of this size "
+    ap.add_argument("--designs", choices=["w1024", "w2048", "besolix-w1024", "besolix-w2048", "pitolix-w1024", "pitolix-w2048", "buzarax-w1024", "buzarax-w2048"], default=None,
+                    help="instead of the benchmark: prefill and decode of a Turudra (w...), a Besolix (besolix-w...), a Pitolix (pitolix-w...) or a Buzarax (buzarax-w...) model of this size "
                          "beside a dense Llama of equal size")
     ap.add_argument("--designs-models", default="turudra,llama", help=argparse.SUPPRESS)
     ap.add_argument("--designs-phase", choices=["both", "prefill", "decode"], default="both", help=argparse.SUPPRESS)

@@ -1,4 +1,4 @@
-"""Prefill and decode throughput of a Turudra, a Besolix or a Pitolix model beside a dense Llama of equal size, with the time of
+"""Prefill and decode throughput of a Turudra, a Besolix, a Pitolix or a Buzarax model beside a dense Llama of equal size, with the time of
 every kernel family inside the steps (``bench.py --designs``).
 
 Sizes resemble real layers; weights are random.  Both models run through the same engine: one prompt of `tokens` tokens
@@ -20,6 +20,7 @@ import torch
 
 from . import kernels, measure
 from .config.besolix import BesolixConfig
+from .config.buzarax import BuzaraxConfig
 from .config.llama import LlamaConfig
 from .config.pitolix import PitolixConfig
 from .config.turudra import TurudraConfig
@@ -115,6 +116,39 @@ def llama_like_pitolix(size: str, positions: int) -> LlamaConfig:
                                   "max_position_embeddings": positions, "torch_dtype": "bfloat16"})
 
 
+BUZARAX_SIZES = {
+    # name: (width, softmax side (heads, kv heads, head size, rotated elements), decay side (heads, key size, value size), recurrence
+    # (channels, blocks, taps), dense feed-forward, experts, chosen, expert feed-forward, vocab); six layers: the parallel mixer and
+    # the recurrence in turn, dense and routed feed-forwards in turn
+    "buzarax-w1024": (1024, (8, 2, 128, 64), (4, 128, 128), (1280, 5, 4), 2816, 16, 2, 1408, 32000),
+    "buzarax-w2048": (2048, (16, 4, 128, 64), (8, 128, 128), (2560, 10, 4), 5632, 16, 2, 2816, 32000),
+}
+
+
+def buzarax_config(size: str) -> BuzaraxConfig:
+    W, (H, K, D, rot), (rh, rd, rv), (R, B, taps), ff, E, top, eff, vocab = BUZARAX_SIZES[size]
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": eff}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": H, "kv_heads": K, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 50.0,
+                 "rot": {"base": 50000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "right": {"heads": rh, "dim": rd, "vdim": rv, "decay": [1.0 - 2.0 ** -(3 + 5.0 * h / max(rh - 1, 1)) for h in range(rh)]},
+        "left_scale": 0.7, "right_scale": 1.1}}
+    rec = {"type": "rglru", "mixer": {"width": R, "blocks": B, "conv": taps}}
+    layers = [dict(par, mlp=dense), dict(rec, mlp=moe), dict(par, mlp=moe), dict(rec, mlp=dense), dict(par, mlp=dense), dict(rec, mlp=moe)]
+    return BuzaraxConfig.from_dict({"architecture": "Buzarax", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+                                    "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": layers})
+
+
+def llama_like_buzarax(size: str, positions: int) -> LlamaConfig:
+    """A dense decoder of the same width, number of layers and attention heads, its feed-forward as wide as what a token uses."""
+    W, (H, K, D, rot), _, _, ff, E, top, eff, vocab = BUZARAX_SIZES[size]
+    return LlamaConfig.from_dict({"architectures": ["LlamaForCausalLM"], "hidden_size": W, "num_hidden_layers": 6,
+                                  "num_attention_heads": H, "num_key_value_heads": K, "head_dim": D,
+                                  "intermediate_size": (ff + top * eff) // 2, "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+                                  "max_position_embeddings": positions, "torch_dtype": "bfloat16"})
+
+
 FAMILIES = {
     "gemm_tc": "products (tcgen05)", "gemm_tc_deferred": "products (tcgen05)", "gemm_simt": "products (FMA)",
     "finish_plain": "products (tcgen05)", "finish_add_rmsnorm": "norms", "rmsnorm": "norms", "finish_rope_store": "rotation + cache store",
@@ -127,6 +161,8 @@ FAMILIES = {
     "delta": "delta recurrence", "head_norm_gate": "delta recurrence", "qk_norm_rope_store": "rotation + cache store",
     "rmsnorm_act": "norms",
     "sigmoid_gate": "output gates", "stream_step": "stream kernels",
+    "rglru": "gated linear recurrence", "decay_attention": "decay attention recurrence", "norm_add": "norms", "depth_average": "stream kernels",
+    "cast_rows": "stream kernels", "embed_pair": "stream kernels", "last_token": "stream kernels", "rotate_heads": "rotation + cache store",
     "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
 }
 
@@ -259,6 +295,52 @@ def _pitolix_work(cfg, tokens, keys_per_token, decode):
             "output gates": (0.0, by_g)}
 
 
+def _buzarax_work(cfg, tokens, keys_per_token, decode):
+    """(FLOPs, bytes) per kernel family in one step of `tokens` tokens, counted like ``_llama_work``."""
+    W, L = cfg.width, len(cfg.layers)
+    fl_a = by_a = fl_p = by_p = by_n = by_r = fl_g = by_g = fl_d = by_d = fl_e = by_e = by_s = 0.0
+    once = tokens if decode else 1
+    for lay in cfg.layers:
+        m = lay.mixer
+        if m.kind == "parallel":
+            l, r = m.left, m.right
+            hd = max(l.dim, l.vdim)
+            cols = (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim
+            rcols = 2 * r.heads * r.dim + 2 * r.heads * r.vdim
+            per = W * (cols + rcols) + (l.heads * l.vdim + r.heads * r.vdim) * W
+            fl_a += 2.0 * tokens * l.heads * keys_per_token * (l.dim + l.vdim)
+            by_a += once * keys_per_token * 2 * l.kv_heads * hd * 2
+            # the values turned in place, the norm/rotation/store kernel, the sums turned back
+            by_r += tokens * 2.0 * (2 * l.kv_heads * l.vdim + cols + (l.heads + 2 * l.kv_heads) * hd + 2 * l.heads * hd)
+            # per token and state element: decay and update, read-out; the state once per request and step, the rows in float32
+            fl_d += 4.0 * tokens * r.heads * r.dim * r.vdim
+            by_d += once * 2 * r.heads * r.dim * r.vdim * 4 + tokens * (rcols * 4 + r.heads * r.vdim * (4 + 4 + 2))
+        else:
+            Bs = m.width // m.blocks
+            per = W * 2 * m.width + m.width * W
+            fl_g += tokens * (4.0 * m.width * Bs + 40.0 * m.width)
+            by_g += tokens * m.width * (2 * 4 + 4 * 4 + 2) + 2 * m.width * Bs * 4
+        f = lay.mlp
+        if f is not None and f.kind == "dense":
+            per += 3 * W * f.ff
+        elif f is not None:
+            fl_e += 2.0 * tokens * f.top * 3 * f.ff * W
+            by_e += min(f.experts, tokens * f.top) * 3 * f.ff * W * 2
+            per += f.experts * W
+        fl_p += 2.0 * tokens * per
+        by_p += 2.0 * per
+        # two output norms a layer read a float32 sum and the stream and write the stream (and a rounded copy)
+        by_n += tokens * W * (4 + 4 + 4 + 2) * (2 if f is not None else 1)
+    fl_p += 2.0 * cfg.vocab * W * (tokens if decode else 1)
+    by_p += 2.0 * cfg.vocab * W
+    by_n += tokens * W * (4 + 2)
+    # the depth averages: layer i reads i + 2 streams and writes two (and a rounded copy); the embedding and its copy
+    by_s = tokens * W * 4.0 * (sum(i + 2 + 2 for i in range(L)) + 3) + tokens * W * 2.0 * L
+    return {"attention": (fl_a, by_a), "products (tcgen05)": (fl_p, by_p), "norms": (0.0, by_n), "rotation + cache store": (0.0, by_r),
+            "gated linear recurrence": (fl_g, by_g), "decay attention recurrence": (fl_d, by_d), "grouped products (experts, per-head)": (fl_e, by_e),
+            "stream kernels": (0.0, by_s)}
+
+
 def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: int, warmup: int, pk, phase: str = "both") -> dict:
     vocab = eng.plan.vocab_size
     gen = torch.Generator().manual_seed(0)
@@ -345,7 +427,9 @@ def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, 
     pool = batch * (context + 64 * (2 + (steps + warmup + 8) // 64)) + tokens + 64
     ep = lambda: EngineParams(dtype="bfloat16", max_tokens=pool, page_size=64, max_requests=batch + 1,
                               max_request_tokens=max(tokens, context + steps + warmup + 72), max_step_tokens=tokens)
-    if size in PITOLIX_SIZES:
+    if size in BUZARAX_SIZES:
+        arms = (("buzarax", buzarax_config(size), _buzarax_work), ("llama", llama_like_buzarax(size, context + tokens), _llama_work))
+    elif size in PITOLIX_SIZES:
         arms = (("pitolix", pitolix_config(size), _pitolix_work), ("llama", llama_like_pitolix(size, context + tokens), _llama_work))
     elif size in BESOLIX_SIZES:
         arms = (("besolix", besolix_config(size), _besolix_work), ("llama", llama_like_besolix(size, context + tokens), _llama_work))
@@ -354,7 +438,7 @@ def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, 
         arms = (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work))
     for name, cfg, work in arms:
         # (`models` names arms to run; "turudra" also stands for the new design's arm of a Besolix size: the default runs both arms)
-        if name not in models and not (name in ("besolix", "pitolix") and "turudra" in models):
+        if name not in models and not (name in ("besolix", "pitolix", "buzarax") and "turudra" in models):
             continue
         t0 = time.perf_counter()
         eng = random_engine(cfg, 5, ep())

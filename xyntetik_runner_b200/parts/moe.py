@@ -96,7 +96,10 @@ class RoutedExperts(FeedForward):
         self.router.forward(h, z)
         ids = ctx.buf("moe_ids", (n, top), torch.int32)
         wts = ctx.buf("moe_weights", (n, top), torch.float32)
-        kernels.route_topk(z, ids, wts, top, self.sigmoid, self.correction)
+        if self.sigmoid:
+            kernels.route_topk(z, ids, wts, top, sigmoid_scores=True, correction=self.correction)
+        else:
+            kernels.route_topk(z, ids, wts, top)
         align = self._row_tile(pairs, E) if self.tensor_cores else kernels.moe_tile_rows()
         max_tiles = kernels.moe_max_tiles(pairs, E, align)
         rows = max_tiles * align
