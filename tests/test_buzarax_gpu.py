@@ -106,15 +106,17 @@ def test_a_batch_gives_what_each_request_gives_alone(models):
         assert np.abs(batch[rid] - alone[rid]).max() <= 2e-5 * scale, rid
 
 
-def test_recurrences_do_not_depend_on_the_cutting_at_all(models):
-    """A model of recurrences alone walks token by token: bit for bit the same logits however a request was cut."""
+def test_recurrences_depend_on_the_cutting_by_the_last_bits_only(models):
+    """A model of recurrences alone walks token by token; only the gates' sums are added in another order in steps of few tokens
+    than in steps of many: the logits of any two cuttings agree to a few units in the last place."""
     path, cfg, tensors, reqs, ref = models["rec"]
     outs = []
     for cut in ("whole", "pairs", "mixed"):
         steps = CUTS[cut](reqs)
         outs.append(traces.collect(steps, run(path, "float32", steps, PAGE["rec"])[0], cfg["vocab"]))
     for rid in reqs:
-        assert np.array_equal(outs[0][rid], outs[1][rid]) and np.array_equal(outs[0][rid], outs[2][rid]), rid
+        scale = np.abs(outs[0][rid]).max()
+        assert np.abs(outs[0][rid] - outs[1][rid]).max() <= 2e-6 * scale and np.abs(outs[0][rid] - outs[2][rid]).max() <= 2e-6 * scale, rid
 
 
 def test_long_decoding_and_first_tokens(models):
@@ -217,7 +219,7 @@ def test_recurrence_kernel_from_states_in_other_slots(R, B, taps):
     want = [plain(pre[:lens[0]]), plain(pre[lens[0]:])]
     state = torch.randn(4, kernels.rglru_state_floats(R, taps) + 3, generator=g).cuda()          # (rows wider than needed, filled with noise)
     state[2].zero_(); state[0].zero_()
-    args = [_dev(w["conv"]), _dev(w["conv.b"]), _dev(w["ra"].transpose(1, 2)), _dev(w["ri"].transpose(1, 2)), _dev(w["ra.b"].reshape(-1)),
+    args = [_dev(w["conv"]), _dev(w["conv.b"]), _dev(w["ra"].transpose(1, 2)), _dev(w["ri"].transpose(1, 2)), _dev(w["ra"]), _dev(w["ri"]), _dev(w["ra.b"].reshape(-1)),
             _dev(w["ri.b"].reshape(-1)), _dev(w["lam"])]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
     # first launch: 12 tokens of the first sequence into slot 2

@@ -129,6 +129,18 @@ static inline void xr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same launch without the attribute: the kernel starts when the kernel ahead of it in the stream is complete, whatever that
+// kernel released.  For a few long-lived blocks (a walk over a long portion's tokens): let in early, they settle several to an SM
+// wherever the kernel ahead leaves room first and stay there, and the walk takes several times as long.
+template <typename... KArgs, typename... Args>
+static inline void xr_launch_behind(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int xr_launch_status() {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) fprintf(stderr, "[xrb200] the runtime refused a launch: %s\n", cudaGetErrorString(e));

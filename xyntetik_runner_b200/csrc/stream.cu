@@ -75,34 +75,63 @@ XR_EXPORT int xr_last_token(const int* ids, const int* feed, int n_feed, const i
 // Norm on a sublayer's output, added into the stream: x[t] += d[t] / sqrt(mean(d[t]^2) + eps) * g, g ONE number (read from the
 // device).  With `cast` the updated row is also written in the activation dtype, for a sublayer that reads the stream as it is.
 // With `clear`, d[t] is zeroed behind the read, ready for the next sublayer's products to add into.
-// One block per row; float32 throughout; the order of the sums depends on the width only.
+// `partial` (float32 [splits][n][width], or null): the sublayer's last products were cut along K and left their partial sums;
+// the row is then d[t] plus the partial sums in split order (plus `bias` [width], if any).
+// One block per row; the row is held in registers between the two passes (up to NA_OWN * 256 columns, more are read again);
+// float32 throughout; the order of the sums depends on the width and the cut only.
 // ---------------------------------------------------------------------------
+#define NA_OWN 16
 template <typename T>
 __global__ void __launch_bounds__(256)
-k_norm_add(float* __restrict__ d, float* __restrict__ x, const float* __restrict__ g, T* __restrict__ cast, int width, float eps, int clear) {
+k_norm_add(float* __restrict__ d, float* __restrict__ x, const float* __restrict__ g, T* __restrict__ cast, int width, float eps, int clear,
+           const float* __restrict__ partial, const float* __restrict__ bias, int splits, int n) {
     xr_pdl_launch();
     __shared__ float scratch[33];
     const float gain = g[0];
     xr_pdl_wait();
-    float* dr = d + (size_t)blockIdx.x * width;
-    float* xr = x + (size_t)blockIdx.x * width;
+    const size_t row = (size_t)blockIdx.x * width, split_stride = (size_t)n * width;
+    float* dr = d + row;
+    float* xr = x + row;
+    auto value = [&](int i) -> float {
+        float v = dr[i];
+        if (partial != nullptr) {
+            for (int s2 = 0; s2 < splits; s2++) v += __ldcg(partial + (size_t)s2 * split_stride + row + i);
+            if (bias != nullptr) v += bias[i];
+        }
+        return v;
+    };
+    float own[NA_OWN];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = dr[i]; ss = fmaf(v, v, ss); }
+#pragma unroll
+    for (int k = 0; k < NA_OWN; k++) {
+        const int i = threadIdx.x + k * 256;
+        own[k] = i < width ? value(i) : 0.f;
+        ss = fmaf(own[k], own[k], ss);
+    }
+    for (int i = threadIdx.x + NA_OWN * 256; i < width; i += 256) { const float v = value(i); ss = fmaf(v, v, ss); }
     ss = xr_block_sum(ss, scratch);
     const float inv = gain / sqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = fmaf(dr[i], inv, xr[i]);
+    auto finish = [&](int i, float dv) {
+        const float v = fmaf(dv, inv, xr[i]);
         xr[i] = v;
-        if (cast != nullptr) cast[(size_t)blockIdx.x * width + i] = xr_from_f32<T>(v);
+        if (cast != nullptr) cast[row + i] = xr_from_f32<T>(v);
         if (clear) dr[i] = 0.f;
+    };
+#pragma unroll
+    for (int k = 0; k < NA_OWN; k++) {
+        const int i = threadIdx.x + k * 256;
+        if (i < width) finish(i, own[k]);
     }
+    for (int i = threadIdx.x + NA_OWN * 256; i < width; i += 256) finish(i, value(i));
 }
 
 XR_EXPORT int xr_norm_add(float* d, float* x, const float* g, void* cast, int cast_dtype, int n, int width, float eps, int clear,
-                          cudaStream_t stream) {
-    if (n < 1 || width < 1) return XR_ERR_ARG;
-    if (cast == nullptr || cast_dtype == XR_F32) xr_launch((k_norm_add<float>), dim3(n), dim3(256), 0, stream, d, x, g, (float*)cast, width, eps, clear);
-    else if (cast_dtype == XR_BF16) xr_launch((k_norm_add<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, d, x, g, (__nv_bfloat16*)cast, width, eps, clear);
+                          const float* partial, const float* bias, int splits, cudaStream_t stream) {
+    if (n < 1 || width < 1 || (partial != nullptr && splits < 1)) return XR_ERR_ARG;
+    if (cast == nullptr || cast_dtype == XR_F32)
+        xr_launch((k_norm_add<float>), dim3(n), dim3(256), 0, stream, d, x, g, (float*)cast, width, eps, clear, partial, bias, splits, n);
+    else if (cast_dtype == XR_BF16)
+        xr_launch((k_norm_add<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, d, x, g, (__nv_bfloat16*)cast, width, eps, clear, partial, bias, splits, n);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

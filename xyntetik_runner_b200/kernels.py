@@ -96,13 +96,13 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_embed_pair": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp],
         "xr_last_token": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp],
-        "xr_norm_add": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+        "xr_norm_add": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp],
         "xr_cast_rows": [_vp, _vp, _i, _ll, _vp],
         "xr_depth_average": [_vp, _vp, _vp, _vp, _vp, _i, _i, _ll, _vp],
         "xr_rotate_heads": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp],
-        "xr_rglru": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+        "xr_rglru": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                      _f, _vp],
-        "xr_decay_attention": [_vp, _ll, _i, _i, _i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "xr_decay_attention": [_vp, _ll, _i, _i, _i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -1040,15 +1040,19 @@ def last_token(ids, seg_start, seg_len, seg_slot, last: torch.Tensor, n_seg: int
     _count()
 
 
-def norm_add(d: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, cast: Optional[torch.Tensor] = None, clear: bool = False) -> None:
+def norm_add(d: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, cast: Optional[torch.Tensor] = None, clear: bool = False,
+             partial: Optional[torch.Tensor] = None, splits: int = 0, bias: Optional[torch.Tensor] = None) -> None:
     """x[t] += d[t] / sqrt(mean(d[t]^2) + eps) * gain (one float32 number on the device); `cast` also receives the new x in its
-    dtype; `clear` zeroes d behind the read."""
-    _dev(d, x, gain, cast)
+    dtype; `clear` zeroes d behind the read.  `partial` (float32 [splits][n][width], with `bias`): partial sums of products cut
+    along K that belong to d; the kernel adds them (split order, then the bias) to d's rows before it takes the norm."""
+    _dev(d, x, gain, cast, partial, bias)
+    assert partial is None or (partial.dtype == torch.float32 and splits >= 1 and partial.numel() >= splits * d.numel())
+    assert bias is None or (partial is not None and bias.dtype == torch.float32 and bias.numel() == d.shape[1])
     n, w = x.shape
     assert d.shape == (n, w) and d.dtype == torch.float32 and x.dtype == torch.float32 and gain.dtype == torch.float32 and gain.numel() == 1
     assert cast is None or cast.shape == (n, w)
     _check(lib().xr_norm_add(d.data_ptr(), x.data_ptr(), gain.data_ptr(), _ptr(cast), 0 if cast is None else dtype_code(cast.dtype), n, w,
-                             float(eps), int(clear), _stream()), "norm_add")
+                             float(eps), int(clear), _ptr(partial), _ptr(bias), int(splits), _stream()), "norm_add")
     _count()
 
 
@@ -1089,20 +1093,21 @@ def rglru_state_floats(R: int, taps: int) -> int:
     return R * taps
 
 
-def rglru(proj: torch.Tensor, conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state: torch.Tensor, tok_seg, seg_start, seg_len, seg_slot,
+def rglru(proj: torch.Tensor, conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state: torch.Tensor, tok_seg, seg_start, seg_len, seg_slot,
           a_s: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor, n_seg: int, R: int, B: int, taps: int, c: float) -> None:
     """The real-gated linear recurrent unit over the step's tokens, request by request, from and into `state`.  proj [n, >= 2R]
     float32 (rows may be strided): the gated branch's pre-activations in columns [0, R), the convolution's inputs in [R, 2R).
-    out [n, R] = S * gelu_tanh(gated branch).  See csrc/recurrent.cu for the other arguments."""
-    _dev(conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state, tok_seg, seg_start, seg_len, seg_slot, a_s, b_s, out)
+    out [n, R] = S * gelu_tanh(gated branch).  wa, wi: the gates' matrices [B, out, in]; wa_t, wi_t: the same transposed to
+    [B, in, out] (steps of many tokens read those).  See csrc/recurrent.cu for the other arguments."""
+    _dev(conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state, tok_seg, seg_start, seg_len, seg_slot, a_s, b_s, out)
     n = proj.shape[0]
     Bs = R // B
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= 2 * R and out.shape == (n, R)
-    assert all(t.dtype == torch.float32 for t in (conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state, a_s, b_s))
-    assert conv_w.shape == (R, taps) and wa_t.shape == (B, Bs, Bs) and wi_t.shape == (B, Bs, Bs) and a_s.numel() >= n * R and b_s.numel() >= n * R
+    assert all(t.dtype == torch.float32 for t in (conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state, a_s, b_s))
+    assert conv_w.shape == (R, taps) and all(t.shape == (B, Bs, Bs) for t in (wa_t, wi_t, wa, wi)) and a_s.numel() >= n * R and b_s.numel() >= n * R
     assert state.dim() == 2 and state.shape[1] >= rglru_state_floats(R, taps)
     _check(lib().xr_rglru(proj.data_ptr(), proj.stride(0), 0, R, conv_w.data_ptr(), conv_b.data_ptr(), wa_t.data_ptr(), wi_t.data_ptr(),
-                          ba.data_ptr(), bi.data_ptr(), lam.data_ptr(), state.data_ptr(), state.stride(0), tok_seg.data_ptr(),
+                          wa.data_ptr(), wi.data_ptr(), ba.data_ptr(), bi.data_ptr(), lam.data_ptr(), state.data_ptr(), state.stride(0), tok_seg.data_ptr(),
                           seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), out.data_ptr(),
                           dtype_code(out.dtype), n, n_seg, R, B, taps, float(c), _stream()), "rglru")
     _count(2)
@@ -1111,12 +1116,13 @@ def rglru(proj: torch.Tensor, conv_w, conv_b, wa_t, wi_t, ba, bi, lam, state: to
 def decay_attention(proj: torch.Tensor, cols, decay: torch.Tensor, state: torch.Tensor, seg_start, seg_len, seg_slot, o: torch.Tensor,
                     n_seg: int, H: int, D: int, V: int) -> None:
     """Linear attention with a constant decay per head: S <- decay_h S + k v^T, o = S^T q, with q, k, v = silu of proj's columns at
-    cols = (q, k, v); proj float32 [n, *], state float32 [slots, >= H D V], o float32 [n, H V]."""
+    cols = (q, k, v); proj float32 [n, *] (a step of many tokens activates those columns in place), state float32 [slots, >= H D V],
+    o float32 [n, H V]."""
     _dev(decay, state, seg_start, seg_len, seg_slot, o)
     n = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and o.shape == (n, H * V) and o.dtype == torch.float32
     assert decay.dtype == torch.float32 and decay.numel() == H and state.dtype == torch.float32 and state.shape[1] >= H * D * V
     _check(lib().xr_decay_attention(proj.data_ptr(), proj.stride(0), cols[0], cols[1], cols[2], decay.data_ptr(), state.data_ptr(),
-                                    state.stride(0), seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), o.data_ptr(), n_seg, H, D, V,
+                                    state.stride(0), seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), o.data_ptr(), n, n_seg, H, D, V,
                                     _stream()), "decay_attention")
-    _count()
+    _count(2 if n > 16 else 1)

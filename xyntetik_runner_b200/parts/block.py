@@ -162,15 +162,25 @@ class OutputNormBlock(Block):
                 kernels.cast_rows(x, h)
         ctx.stream_cast = None
         d = ctx.buf("block_sum", (n, width), torch.float32)
-        d.zero_()
+        # the sum starts at zero once a step; every norm clears it behind its read
+        ctx.once(("output_norm_sum", d.data_ptr()), lambda: (d.zero_(), True)[1])
         self.mixer.forward(ctx, h, d, lay)
-        ctx.materialize(d)
         last = self.feed_forward is None
-        kernels.norm_add(d, x, self.mixer_norm.gain, self.mixer_norm.eps, cast=h if narrow and not last else None, clear=not last)
+        self._norm_add(ctx, d, x, self.mixer_norm, cast=h if narrow and not last else None)
         if not last:
             self.feed_forward.forward(ctx, h, d)
-            ctx.materialize(d)
-            kernels.norm_add(d, x, self.ff_norm.gain, self.ff_norm.eps)
+            self._norm_add(ctx, d, x, self.ff_norm, cast=None)
+
+    @staticmethod
+    def _norm_add(ctx, d, x, norm, cast):
+        """x += norm(d); partial sums that the sublayer's last products left on d are taken in the same pass."""
+        from .. import kernels
+        pend = ctx.take_pending(d)
+        if pend is None:
+            kernels.norm_add(d, x, norm.gain, norm.eps, cast=cast, clear=True)
+            return
+        kernels.norm_add(d, x, norm.gain, norm.eps, cast=cast, clear=True, partial=pend.partial, splits=pend.splits, bias=pend.bias)
+        pend.release()
 
 
 register_block("output_norm", OutputNormBlock)

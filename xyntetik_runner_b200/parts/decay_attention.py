@@ -27,8 +27,8 @@ class DecayLinearAttention(Mixer):
                  out_scale: float = 1.0, q: str = "q", k: str = "k", v: str = "v", g: str = "g", o: str = "o", norm: str = "norm"):
         if len(decay) != heads:
             raise ValueError(f"{prefix}: {len(decay)} decays for {heads} heads")
-        if dim > 512:
-            raise ValueError(f"{prefix}: key size {dim}: the recurrence kernel takes up to 512")
+        if dim > 256:
+            raise ValueError(f"{prefix}: key size {dim}: the recurrence kernel takes up to 256")
         self.width, self.H, self.D, self.V = width, heads, dim, vdim
         self.decay_values, self.eps, self.prefix, self.out_scale = [float(d) for d in decay], float(eps), prefix, float(out_scale)
         self.names = {a: prefix + b for a, b in dict(q=q, k=k, v=v, g=g, o=o, norm=norm).items()}
@@ -59,8 +59,7 @@ class DecayLinearAttention(Mixer):
     def forward(self, ctx, h, x, lay):
         n, H, D, V = h.shape[0], self.H, self.D, self.V
         total = 2 * H * D + 2 * H * V
-        ld = -(-total // 8) * 8
-        proj = ctx.buf("decay_proj", (n, ld), torch.float32)[:, :total]
+        proj = ctx.buf("decay_proj", (n, -(-total // 8) * 8), torch.float32)[:, :total]
         self.proj.forward(h, proj)
         o = ctx.buf("decay_o", (n, H * V), torch.float32)
         kernels.decay_attention(proj, (0, H * D, 2 * H * D), self.decay, lay.state, ctx.seg_start, ctx.seg_len, ctx.seg_slot, o,

@@ -60,8 +60,9 @@ class GatedLinearRecurrence(Mixer):
         self.out = Linear(tensors[n["o"]]).prepare(rt)
         self.conv_w, self.conv_b = f32(n["conv"]), f32(n["conv"] + b)
         # the gates' matrices transposed, [block][in][out]: a warp then reads consecutive outputs of one input
-        self.wa_t = f32(n["ra"]).transpose(1, 2).contiguous()
-        self.wi_t = f32(n["ri"]).transpose(1, 2).contiguous()
+        self.wa, self.wi = f32(n["ra"]), f32(n["ri"])
+        self.wa_t = self.wa.transpose(1, 2).contiguous()
+        self.wi_t = self.wi.transpose(1, 2).contiguous()
         self.ba, self.bi, self.lam = f32(n["ra"] + b).reshape(-1), f32(n["ri"] + b).reshape(-1), f32(n["lam"])
         self._small = (self.wa_t.numel() + self.wi_t.numel() + self.conv_w.numel() + 4 * self.R) * 4
 
@@ -76,7 +77,7 @@ class GatedLinearRecurrence(Mixer):
         a_s = ctx.buf("rglru_a", (n, R), torch.float32)
         b_s = ctx.buf("rglru_b", (n, R), torch.float32)
         y = ctx.buf("rglru_out", (n, R), ctx.act_dtype)
-        kernels.rglru(proj, self.conv_w, self.conv_b, self.wa_t, self.wi_t, self.ba, self.bi, self.lam, lay.state, ctx.tok_seg,
+        kernels.rglru(proj, self.conv_w, self.conv_b, self.wa_t, self.wi_t, self.wa, self.wi, self.ba, self.bi, self.lam, lay.state, ctx.tok_seg,
                       ctx.seg_start, ctx.seg_len, ctx.seg_slot, a_s, b_s, y, ctx.n_seg, R, self.B, self.taps, self.rate)
         ctx.set_pending(x, self.out.forward(y, x, accumulate=True, defer=True))
 
