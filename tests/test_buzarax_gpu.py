@@ -229,9 +229,9 @@ def test_recurrence_kernel_from_states_in_other_slots(R, B, taps):
             (torch.cat([pre[lens[0]:], pre[n0:lens[0]]]), [0] * lens[1] + [1] * (lens[0] - n0), [0, lens[1]], [lens[1], lens[0] - n0], [0, 2],
              [(1, 0, lens[1]), (0, n0, lens[0])])):
         n = rows.shape[0]
-        a_s, b_s = torch.empty(n, R).cuda(), torch.empty(n, R).cuda()
+        a_s, b_s, u_s = torch.empty(n, R).cuda(), torch.empty(n, R).cuda(), torch.empty(n, R).cuda()
         out = torch.empty(n, R).cuda()
-        kernels.rglru(_dev(rows), *args, state, i32(tok_seg), i32(starts), i32(lns), i32(slots), a_s, b_s, out, len(starts), R, B, taps, 8.0)
+        kernels.rglru(_dev(rows), *args, state, i32(tok_seg), i32(starts), i32(lns), i32(slots), a_s, b_s, u_s, out, len(starts), R, B, taps, 8.0)
         at = 0
         for (which, lo, hi), ln in zip(checks, lns):
             got = out[at:at + ln].double().cpu()
@@ -276,7 +276,7 @@ def test_decay_attention_kernel_cut_against_whole(H, D, V):
     assert torch.allclose(outs[0].double(), want, rtol=2e-5, atol=1e-5)
     # and the whole mixer's tail (norm over all heads, gate) against the plain function
     y = torch.empty(T, H * V).cuda()
-    kernels.head_norm_gate(outs[0].cuda(), _dev(pre), 2 * H * D + H * V, torch.ones(H * V).cuda(), y, 1, H * V, 1e-5, scale=0.75)
+    kernels.row_norm_gate(outs[0].cuda(), _dev(pre), 2 * H * D + H * V, torch.ones(H * V).cuda(), y, 1e-5, scale=0.75)
     full = P.decayed_linear_attention(pre.double(), {n: t.double() for n, t in w.items()}, {"heads": H, "dim": D, "vdim": V, "decay": decay.tolist()}, 1e-5)
     assert torch.allclose(y.double().cpu(), 0.75 * full, rtol=1e-4, atol=1e-5)
 

@@ -268,7 +268,7 @@ k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, in
 template <typename T, typename TG = T>
 __global__ void __launch_bounds__(128)
 k_mlstm_out(const float* __restrict__ o, const TG* __restrict__ proj, long long ldp, int g_col, const float* __restrict__ w,
-            T* __restrict__ y, int n, int H, int V, float eps, int w_head, int gate_silu, float out_scale) {
+            T* __restrict__ y, int n, int H, int V, float eps, int w_head, int gate_silu) {
     xr_pdl_launch();
     xr_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -279,7 +279,7 @@ k_mlstm_out(const float* __restrict__ o, const TG* __restrict__ proj, long long 
     float ss = 0.f;
     for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
     ss = xr_warp_sum(ss);
-    const float inv = out_scale / sqrtf(ss / (float)V + eps);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
     const TG* g = proj + (size_t)t * ldp + g_col + (size_t)h * V;
     T* dst = y + (size_t)t * H * V + (size_t)h * V;
     for (int i = lane; i < V; i += 32) {
@@ -327,7 +327,7 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
                   seg_len, seg_slot, H, D, V, cap, stage);                                                                            \
         SCAN(T);                                                                                                                      \
         xr_launch((k_mlstm_out<T>), dim3(gb), dim3(128), 0, stream, (const float*)o, (const T*)proj, ldp, g_col, norm_w, (T*)y, n, H, \
-                  V, eps, V, 0, 1.0f);                                                                                                       \
+                  V, eps, V, 0);                                                                                                         \
     } while (0)
     if (dtype == XR_F32) ML(float);
     else if (dtype == XR_BF16) ML(__nv_bfloat16);
@@ -340,19 +340,19 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
 
 // The last step alone, for other recurrences: y [n][H * V] (dtype `dtype`) = o / rms(o per head) * w * act(gate), gate [n][ld_gate]
 // (dtype `gate_dtype`: that of y, or float32) from column 0, head h at h * V; w_head: elements between the heads' weights (0: one
-// weight for all heads); `scale` multiplies the result.  (H = 1 norms a whole row at once.)
+// weight for all heads).
 XR_EXPORT int xr_head_norm_gate(const float* o, const void* gate, int gate_dtype, long long ld_gate, const float* w, int w_head, int gate_silu,
-                                void* y, int dtype, int n, int H, int V, float eps, float scale, cudaStream_t stream) {
+                                void* y, int dtype, int n, int H, int V, float eps, cudaStream_t stream) {
     if (n < 1 || H < 1 || V < 1 || w_head < 0) return XR_ERR_ARG;
     const long long warps = (long long)n * H;
     const unsigned gb = (unsigned)((warps + 3) / 4);
     typedef __nv_bfloat16 bf;
     if (dtype == XR_F32 && gate_dtype == XR_F32)
-        xr_launch((k_mlstm_out<float, float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (float*)y, n, H, V, eps, w_head, gate_silu, scale);
+        xr_launch((k_mlstm_out<float, float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (float*)y, n, H, V, eps, w_head, gate_silu);
     else if (dtype == XR_BF16 && gate_dtype == XR_BF16)
-        xr_launch((k_mlstm_out<bf, bf>), dim3(gb), dim3(128), 0, stream, o, (const bf*)gate, ld_gate, 0, w, (bf*)y, n, H, V, eps, w_head, gate_silu, scale);
+        xr_launch((k_mlstm_out<bf, bf>), dim3(gb), dim3(128), 0, stream, o, (const bf*)gate, ld_gate, 0, w, (bf*)y, n, H, V, eps, w_head, gate_silu);
     else if (dtype == XR_BF16 && gate_dtype == XR_F32)
-        xr_launch((k_mlstm_out<bf, float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (bf*)y, n, H, V, eps, w_head, gate_silu, scale);
+        xr_launch((k_mlstm_out<bf, float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (bf*)y, n, H, V, eps, w_head, gate_silu);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

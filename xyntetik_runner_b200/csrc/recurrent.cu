@@ -126,6 +126,29 @@ k_rglru_gates(float* __restrict__ proj, long long ldp, int y_col, int x_col, con
     }
 }
 
+// The convolution alone, a thread an element: u [n][R].  Ahead of k_rglru_gates_few, whose many small blocks would each compute
+// the whole tile again behind a chain of dependent loads.
+__global__ void k_rglru_conv(const float* __restrict__ proj, long long ldp, int x_col, const float* __restrict__ conv_w,
+                             const float* __restrict__ conv_b, const float* __restrict__ state, long long state_stride,
+                             const int* __restrict__ tok_seg, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                             float* __restrict__ u, int n, int R, int taps) {
+    xr_pdl_launch();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * R) return;
+    const int t = idx / R, ch = idx % R;
+    const int seg = tok_seg[t], i = t - seg_start[seg];
+    const float* tail = state + (size_t)seg_slot[seg] * state_stride + R;
+    const float* w = conv_w + (size_t)ch * taps;
+    float acc = conv_b[ch];
+    xr_pdl_wait();
+    for (int j = taps - 1; j >= 0; j--) {                            // oldest input first
+        const int ip = i - j;
+        const float x = ip >= 0 ? proj[(size_t)(t - j) * ldp + x_col + ch] : tail[(size_t)(taps - 1 + ip) * R + ch];
+        acc = fmaf(w[taps - 1 - j], x, acc);
+    }
+    u[idx] = acc;
+}
+
 // Few tokens (a step of single tokens): a warp an output channel, its lanes share the inputs, so that the matrices' rows (as
 // stored, [b][out][in]) are read by whole warps and every load of a thread is in flight at once.  A block: 8 tokens, 8 channels.
 __global__ void __launch_bounds__(256)
@@ -133,7 +156,7 @@ k_rglru_gates_few(float* __restrict__ proj, long long ldp, int y_col, int x_col,
                   const float* __restrict__ wa, const float* __restrict__ wi, const float* __restrict__ ba, const float* __restrict__ bi,
                   const float* __restrict__ lam, const float* __restrict__ state, long long state_stride, const int* __restrict__ tok_seg,
                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ a_out, float* __restrict__ b_out,
-                  int n, int R, int Bs, int taps, float c, int groups) {
+                  int n, int R, int Bs, int taps, float c, int groups, const float* __restrict__ u_in) {
     xr_pdl_launch();
     extern __shared__ __align__(16) float rg_u[];                // [8][Bs]
     const int t0 = blockIdx.x * 8, b = blockIdx.y / groups, c0 = b * Bs;
@@ -141,7 +164,7 @@ k_rglru_gates_few(float* __restrict__ proj, long long ldp, int y_col, int x_col,
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int o = (blockIdx.y % groups) * 8 + warp;
     xr_pdl_wait();
-    rg_conv_tile(rg_u, 1, Bs, (const float*)proj, ldp, x_col, conv_w, conv_b, state, state_stride, tok_seg, seg_start, seg_slot, t0, nt, c0, R, Bs, taps);
+    for (int idx = threadIdx.x; idx < nt * Bs; idx += blockDim.x) rg_u[idx] = u_in[(size_t)(t0 + idx / Bs) * R + c0 + idx % Bs];
     __syncthreads();
     if (o >= Bs) return;
     const float* rowa = wa + ((size_t)b * Bs + o) * Bs;
@@ -223,10 +246,10 @@ k_rglru_scan(const float* __restrict__ proj, long long ldp, int y_col, int x_col
 // proj [n][ldp] float32: the gated branch's pre-activations at y_col, the convolution's inputs at x_col, R columns each.
 // conv_w [R][taps], conv_b [R]; wa_t, wi_t [B][R/B (in)][R/B (out)] and wa, wi the same matrices as stored, [B][out][in]; ba, bi,
 // lam [R]; all float32.
-// state [slots][state_stride] float32: S [R], tail [taps-1][R].  a_s, b_s [n][R] float32 scratch.  out [n][R] dtype `dtype`.
+// state [slots][state_stride] float32: S [R], tail [taps-1][R].  a_s, b_s, u_s [n][R] float32 scratch.  out [n][R] dtype `dtype`.
 XR_EXPORT int xr_rglru(float* proj, long long ldp, int y_col, int x_col, const float* conv_w, const float* conv_b, const float* wa_t,
                        const float* wi_t, const float* wa, const float* wi, const float* ba, const float* bi, const float* lam, float* state, long long state_stride,
-                       const int* tok_seg, const int* seg_start, const int* seg_len, const int* seg_slot, float* a_s, float* b_s, void* out,
+                       const int* tok_seg, const int* seg_start, const int* seg_len, const int* seg_slot, float* a_s, float* b_s, float* u_s, void* out,
                        int dtype, int n, int n_seg, int R, int B, int taps, float c, cudaStream_t stream) {
     if (n < 1 || n_seg < 1 || R < 1 || B < 1 || R % B || taps < 1 || taps > RG_MAX_TAPS || n_seg > 65535 || B > 65535 ||
         state_stride < (long long)R * taps)
@@ -236,7 +259,10 @@ XR_EXPORT int xr_rglru(float* proj, long long ldp, int y_col, int x_col, const f
 #define RG_ARGS(A, I) proj, ldp, y_col, x_col, conv_w, conv_b, A, I, ba, bi, lam, (const float*)state, state_stride, tok_seg, seg_start, seg_slot, a_s, b_s, n, R, Bs, taps, c
     if (n <= 16) {
         const int groups = (Bs + 7) / 8;
-        xr_launch(k_rglru_gates_few, dim3((n + 7) / 8, B * groups), dim3(256), (size_t)8 * Bs * sizeof(float), stream, RG_ARGS(wa, wi), groups);
+        xr_launch(k_rglru_conv, dim3((n * R + 255) / 256), dim3(256), 0, stream, (const float*)proj, ldp, x_col, conv_w, conv_b, (const float*)state,
+                  state_stride, tok_seg, seg_start, seg_slot, u_s, n, R, taps);
+        xr_launch(k_rglru_gates_few, dim3((n + 7) / 8, B * groups), dim3(256), (size_t)8 * Bs * sizeof(float), stream, RG_ARGS(wa, wi), groups,
+                  (const float*)u_s);
     } else if (n >= 64 && (size_t)32 * Bs * sizeof(float) <= 48 * 1024) {
         xr_launch((k_rglru_gates<32>), dim3((n + 31) / 32, B, (Bs + RG_COLS - 1) / RG_COLS), dim3(RG_COLS), (size_t)32 * Bs * sizeof(float), stream, RG_ARGS(wa_t, wi_t));
     } else {

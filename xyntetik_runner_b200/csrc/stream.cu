@@ -100,14 +100,37 @@ k_norm_add(float* __restrict__ d, float* __restrict__ x, const float* __restrict
         }
         return v;
     };
+    // a thread's columns of one split are independent loads, all in flight together; the splits are added in their order
     float own[NA_OWN];
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < NA_OWN; k++) {
         const int i = threadIdx.x + k * 256;
-        own[k] = i < width ? value(i) : 0.f;
-        ss = fmaf(own[k], own[k], ss);
+        own[k] = i < width ? dr[i] : 0.f;
     }
+    if (partial != nullptr) {
+#pragma unroll 2
+        for (int s2 = 0; s2 < splits; s2++) {
+            const float* ps = partial + (size_t)s2 * split_stride + row;
+            float v[NA_OWN];
+#pragma unroll
+            for (int k = 0; k < NA_OWN; k++) {
+                const int i = threadIdx.x + k * 256;
+                v[k] = i < width ? xr_ld_now(ps + i) : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < NA_OWN; k++) { xr_ld_fence(v[k]); own[k] += v[k]; }
+        }
+        if (bias != nullptr) {
+#pragma unroll
+            for (int k = 0; k < NA_OWN; k++) {
+                const int i = threadIdx.x + k * 256;
+                if (i < width) own[k] += bias[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NA_OWN; k++) ss = fmaf(own[k], own[k], ss);
     for (int i = threadIdx.x + NA_OWN * 256; i < width; i += 256) { const float v = value(i); ss = fmaf(v, v, ss); }
     ss = xr_block_sum(ss, scratch);
     const float inv = gain / sqrtf(ss / (float)width + eps);
@@ -132,6 +155,36 @@ XR_EXPORT int xr_norm_add(float* d, float* x, const float* g, void* cast, int ca
         xr_launch((k_norm_add<float>), dim3(n), dim3(256), 0, stream, d, x, g, (float*)cast, width, eps, clear, partial, bias, splits, n);
     else if (cast_dtype == XR_BF16)
         xr_launch((k_norm_add<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, d, x, g, (__nv_bfloat16*)cast, width, eps, clear, partial, bias, splits, n);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// A norm over a whole row with a weight per column, times a sigmoid gate: y[t][i] = o[t][i] / sqrt(mean(o[t]^2) + eps) * w[i] *
+// sigmoid(g[t][i]) * scale; o, g float32 (g at g + t * ld_g), y in the activation dtype.  One block per row.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_row_norm_gate(const float* __restrict__ o, const float* __restrict__ g, long long ld_g, const float* __restrict__ w, T* __restrict__ y,
+                int width, float eps, float scale) {
+    xr_pdl_launch();
+    __shared__ float scratch[33];
+    xr_pdl_wait();
+    const float* src = o + (size_t)blockIdx.x * width;
+    const float* gate = g + (size_t)blockIdx.x * ld_g;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = src[i]; ss = fmaf(v, v, ss); }
+    ss = xr_block_sum(ss, scratch);
+    const float inv = scale / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        y[(size_t)blockIdx.x * width + i] = xr_from_f32<T>(src[i] * inv * w[i] / (1.0f + expf(-gate[i])));
+}
+
+XR_EXPORT int xr_row_norm_gate(const float* o, const float* g, long long ld_g, const float* w, void* y, int dtype, int n, int width, float eps,
+                               float scale, cudaStream_t stream) {
+    if (n < 1 || width < 1) return XR_ERR_ARG;
+    if (dtype == XR_F32) xr_launch((k_row_norm_gate<float>), dim3(n), dim3(256), 0, stream, o, g, ld_g, w, (float*)y, width, eps, scale);
+    else if (dtype == XR_BF16) xr_launch((k_row_norm_gate<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, o, g, ld_g, w, (__nv_bfloat16*)y, width, eps, scale);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

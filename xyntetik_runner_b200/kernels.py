@@ -85,7 +85,7 @@ def _declare(L: ctypes.CDLL) -> None:
                                   _vp, _i, _vp, _i, _f, _i, _vp],
         "xr_rmsnorm_act": [_vp, _i, _ll, _vp, _vp, _ll, _i, _i, _f, _vp],
         "xr_delta": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _vp],
+        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
         "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
         "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -100,8 +100,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_cast_rows": [_vp, _vp, _i, _ll, _vp],
         "xr_depth_average": [_vp, _vp, _vp, _vp, _vp, _i, _i, _ll, _vp],
         "xr_rotate_heads": [_vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp],
-        "xr_rglru": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+        "xr_rglru": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                      _f, _vp],
+        "xr_row_norm_gate": [_vp, _vp, _ll, _vp, _vp, _i, _i, _i, _f, _f, _vp],
         "xr_decay_attention": [_vp, _ll, _i, _i, _i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     }
     for name, args in sig.items():
@@ -877,7 +878,7 @@ def mlstm(proj: torch.Tensor, cols, gates: torch.Tensor, state: torch.Tensor, co
 
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.Tensor, y: torch.Tensor, H: int, V: int, eps: float,
-                   per_head_weight: bool = False, silu: bool = False, scale: float = 1.0) -> None:
+                   per_head_weight: bool = False, silu: bool = False) -> None:
     """y [n, H V] = o / rms(o per head) * w * act(gate[:, gate_col + h V + i]): o float32 [n, H V]; y in the activation dtype, gate
     in y's dtype or float32; w float32, V values for all heads or (`per_head_weight`) H V; act the sigmoid, or SiLU with `silu`."""
     _dev(o, w, y)
@@ -887,7 +888,7 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.
     assert w.dtype == torch.float32 and w.numel() == (H * V if per_head_weight else V) and gate.shape[1] >= gate_col + H * V
     _check(lib().xr_head_norm_gate(o.data_ptr(), gate.data_ptr() + gate_col * gate.element_size(), dtype_code(gate.dtype), gate.stride(0),
                                    w.data_ptr(), V if per_head_weight else 0, int(silu), y.data_ptr(), dtype_code(y.dtype), n, H, V,
-                                   float(eps), float(scale), _stream()), "head_norm_gate")
+                                   float(eps), _stream()), "head_norm_gate")
     _count()
 
 
@@ -1056,6 +1057,18 @@ def norm_add(d: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, eps: float, c
     _count()
 
 
+def row_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.Tensor, y: torch.Tensor, eps: float, scale: float = 1.0) -> None:
+    """y[t] = o[t] / sqrt(mean(o[t]^2) + eps) * w * sigmoid(gate[t, gate_col:gate_col + width]) * scale: one norm over the whole row;
+    o, gate, w float32, y in the activation dtype."""
+    _dev(o, w, y)
+    n, width = o.shape
+    assert o.dtype == torch.float32 and gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] >= gate_col + width
+    assert w.dtype == torch.float32 and w.numel() == width and y.shape == (n, width)
+    _check(lib().xr_row_norm_gate(o.data_ptr(), gate.data_ptr() + 4 * gate_col, gate.stride(0), w.data_ptr(), y.data_ptr(), dtype_code(y.dtype),
+                                  n, width, float(eps), float(scale), _stream()), "row_norm_gate")
+    _count()
+
+
 def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
     """out = x in out's dtype (x float32)."""
     _dev(x, out)
@@ -1094,23 +1107,24 @@ def rglru_state_floats(R: int, taps: int) -> int:
 
 
 def rglru(proj: torch.Tensor, conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state: torch.Tensor, tok_seg, seg_start, seg_len, seg_slot,
-          a_s: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor, n_seg: int, R: int, B: int, taps: int, c: float) -> None:
+          a_s: torch.Tensor, b_s: torch.Tensor, u_s: torch.Tensor, out: torch.Tensor, n_seg: int, R: int, B: int, taps: int, c: float) -> None:
     """The real-gated linear recurrent unit over the step's tokens, request by request, from and into `state`.  proj [n, >= 2R]
     float32 (rows may be strided): the gated branch's pre-activations in columns [0, R), the convolution's inputs in [R, 2R).
     out [n, R] = S * gelu_tanh(gated branch).  wa, wi: the gates' matrices [B, out, in]; wa_t, wi_t: the same transposed to
     [B, in, out] (steps of many tokens read those).  See csrc/recurrent.cu for the other arguments."""
-    _dev(conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state, tok_seg, seg_start, seg_len, seg_slot, a_s, b_s, out)
+    _dev(conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state, tok_seg, seg_start, seg_len, seg_slot, a_s, b_s, u_s, out)
     n = proj.shape[0]
     Bs = R // B
+    assert u_s.dtype == torch.float32 and u_s.numel() >= n * R
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= 2 * R and out.shape == (n, R)
     assert all(t.dtype == torch.float32 for t in (conv_w, conv_b, wa_t, wi_t, wa, wi, ba, bi, lam, state, a_s, b_s))
     assert conv_w.shape == (R, taps) and all(t.shape == (B, Bs, Bs) for t in (wa_t, wi_t, wa, wi)) and a_s.numel() >= n * R and b_s.numel() >= n * R
     assert state.dim() == 2 and state.shape[1] >= rglru_state_floats(R, taps)
     _check(lib().xr_rglru(proj.data_ptr(), proj.stride(0), 0, R, conv_w.data_ptr(), conv_b.data_ptr(), wa_t.data_ptr(), wi_t.data_ptr(),
                           wa.data_ptr(), wi.data_ptr(), ba.data_ptr(), bi.data_ptr(), lam.data_ptr(), state.data_ptr(), state.stride(0), tok_seg.data_ptr(),
-                          seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), out.data_ptr(),
+                          seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), u_s.data_ptr(), out.data_ptr(),
                           dtype_code(out.dtype), n, n_seg, R, B, taps, float(c), _stream()), "rglru")
-    _count(2)
+    _count(3 if n <= 16 else 2)
 
 
 def decay_attention(proj: torch.Tensor, cols, decay: torch.Tensor, state: torch.Tensor, seg_start, seg_len, seg_slot, o: torch.Tensor,

@@ -162,7 +162,7 @@ FAMILIES = {
     "rmsnorm_act": "norms",
     "sigmoid_gate": "output gates", "stream_step": "stream kernels",
     "rglru": "gated linear recurrence", "decay_attention": "decay attention recurrence", "norm_add": "norms", "depth_average": "stream kernels",
-    "cast_rows": "stream kernels", "embed_pair": "stream kernels", "last_token": "stream kernels", "rotate_heads": "rotation + cache store",
+    "cast_rows": "stream kernels", "row_norm_gate": "decay attention recurrence", "embed_pair": "stream kernels", "last_token": "stream kernels", "rotate_heads": "rotation + cache store",
     "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
 }
 

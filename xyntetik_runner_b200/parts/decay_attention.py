@@ -65,8 +65,7 @@ class DecayLinearAttention(Mixer):
         kernels.decay_attention(proj, (0, H * D, 2 * H * D), self.decay, lay.state, ctx.seg_start, ctx.seg_len, ctx.seg_slot, o,
                                 ctx.n_seg, H, D, V)
         y = ctx.buf("decay_out", (n, H * V), ctx.act_dtype)
-        # one norm over the whole row: the kernel's "head" is the row
-        kernels.head_norm_gate(o, proj, 2 * H * D + H * V, self.norm_w, y, 1, H * V, self.eps, scale=self.out_scale)
+        kernels.row_norm_gate(o, proj, 2 * H * D + H * V, self.norm_w, y, self.eps, scale=self.out_scale)
         ctx.set_pending(x, self.out.forward(y, x, accumulate=True, defer=True))
 
 

@@ -76,9 +76,10 @@ class GatedLinearRecurrence(Mixer):
         self.proj.forward(h, proj)
         a_s = ctx.buf("rglru_a", (n, R), torch.float32)
         b_s = ctx.buf("rglru_b", (n, R), torch.float32)
+        u_s = ctx.buf("rglru_u", (n, R), torch.float32)
         y = ctx.buf("rglru_out", (n, R), ctx.act_dtype)
         kernels.rglru(proj, self.conv_w, self.conv_b, self.wa_t, self.wi_t, self.wa, self.wi, self.ba, self.bi, self.lam, lay.state, ctx.tok_seg,
-                      ctx.seg_start, ctx.seg_len, ctx.seg_slot, a_s, b_s, y, ctx.n_seg, R, self.B, self.taps, self.rate)
+                      ctx.seg_start, ctx.seg_len, ctx.seg_slot, a_s, b_s, u_s, y, ctx.n_seg, R, self.B, self.taps, self.rate)
         ctx.set_pending(x, self.out.forward(y, x, accumulate=True, defer=True))
 
 
