@@ -197,7 +197,7 @@ def _dev(t, dtype=torch.float32):
     return t.to(dtype).cuda().contiguous()
 
 
-@pytest.mark.parametrize("R,B,taps", [(48, 3, 4), (40, 1, 1), (320, 2, 3), (130, 5, 16)])
+@pytest.mark.parametrize("R,B,taps", [(48, 3, 4), (40, 1, 1), (320, 2, 3), (130, 5, 16), (1800, 1, 2)])
 def test_recurrence_kernel_from_states_in_other_slots(R, B, taps):
     """Two portions in one launch, in slots 2 and 0 of four, one continuing a state and a tail that an earlier launch left."""
     from xyntetik_runner_b200 import kernels

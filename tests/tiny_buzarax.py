@@ -68,11 +68,11 @@ CONFIGS = {
         layer(parallel(5, 5, 10, 14, 0.4, rot(7.0, 10, (2.0, 16, 4.0, 1.0)), None, 1, 20, 4, (0.999,), 0.5, 1.0), dense(28, 4.0))], 7, 2, 9),
     # sizes that the tensor-core kernels take (heads of 64 and 128, pages of 64)
     "tc": model(160, 128, 1e-5, [
-        layer(parallel(4, 2, 64, 64, 0.12, rot(20000.0, 32, (8.0, 128, 32.0, 1.0)), 30.0, 2, 32, 64, (0.95, 0.6), 0.6, 1.1), dense(96, 1.0)),
+        layer(parallel(4, 2, 64, 64, 0.12, rot(20000.0, 32, (6.0, 128, 24.0, 1.5)), 30.0, 2, 32, 64, (0.95, 0.6), 0.55, 1.25), dense(96, 1.0)),
         layer(rglru(256, 2, 3), moe(8, 2, 64)),
-        layer(parallel(2, 1, 128, 128, 0.09, rot(500.0, 64), 50.0, 4, 16, 16, (0.9, 0.8, 0.7, 0.99), 1.0, 1.0), moe(8, 3, 32)),
-        layer(parallel(16, 2, 16, 32, 0.25, rot(100.0, 16, (4.0, 32, 8.0, 2.0)), None, 1, 64, 128, (0.98,), 0.8, 0.9), None)], 97, 31, 7,
-        logit_softcap=15.0),
+        layer(parallel(2, 1, 128, 128, 0.09, rot(500.0, 64), 40.0, 4, 16, 16, (0.9, 0.8, 0.7, 0.99), 1.0, 1.0), moe(8, 3, 32)),
+        layer(parallel(16, 2, 16, 32, 0.25, rot(100.0, 16, (4.0, 32, 8.0, 2.0)), None, 1, 64, 128, (0.98,), 0.8, 0.9), None)], 97, 29, 5,
+        logit_softcap=12.0),
     # recurrences alone (no keys are cached at all), slow ones among them
     "rec": model(90, 64, 1e-5, [
         layer(rglru(64, 4, 3), dense(40, 1.5)),

@@ -34,7 +34,7 @@ __device__ __forceinline__ float rc_softplus(float z) { return z > 30.0f ? z : l
 __device__ __forceinline__ float rc_silu(float z) { return z < -80.0f ? 0.0f : z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float rc_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 
-#define RG_COLS 64               // output channels a block of the gates kernel takes (a thread each)
+#define RG_COLS 128              // output channels a block of the gates kernel takes (a thread each)
 
 // The convolution of tokens t0 .. t0 + nt - 1 over the channels of block b into shared memory; u[e * stride_e + tt * stride_t].
 __device__ __forceinline__ void rg_conv_tile(float* u, int stride_e, int stride_t, const float* __restrict__ proj, long long ldp, int x_col,
@@ -255,18 +255,23 @@ XR_EXPORT int xr_rglru(float* proj, long long ldp, int y_col, int x_col, const f
         state_stride < (long long)R * taps)
         return XR_ERR_ARG;
     const int Bs = R / B;
-    if ((size_t)8 * Bs * sizeof(float) > 48 * 1024) return XR_ERR_ARG;
+    // (a tile of eight tokens of one channel block in shared memory: wide blocks ask for more than the default 48 KB)
+    const size_t smem8 = (size_t)8 * Bs * sizeof(float);
+    if (smem8 > 200 * 1024) return XR_ERR_ARG;
+    if (smem8 > 48 * 1024 &&
+        (cudaFuncSetAttribute(k_rglru_gates_few, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem8) != cudaSuccess ||
+         cudaFuncSetAttribute(k_rglru_gates<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem8) != cudaSuccess))
+        return XR_ERR_LAUNCH;
 #define RG_ARGS(A, I) proj, ldp, y_col, x_col, conv_w, conv_b, A, I, ba, bi, lam, (const float*)state, state_stride, tok_seg, seg_start, seg_slot, a_s, b_s, n, R, Bs, taps, c
     if (n <= 16) {
         const int groups = (Bs + 7) / 8;
         xr_launch(k_rglru_conv, dim3((n * R + 255) / 256), dim3(256), 0, stream, (const float*)proj, ldp, x_col, conv_w, conv_b, (const float*)state,
                   state_stride, tok_seg, seg_start, seg_slot, u_s, n, R, taps);
-        xr_launch(k_rglru_gates_few, dim3((n + 7) / 8, B * groups), dim3(256), (size_t)8 * Bs * sizeof(float), stream, RG_ARGS(wa, wi), groups,
-                  (const float*)u_s);
+        xr_launch(k_rglru_gates_few, dim3((n + 7) / 8, B * groups), dim3(256), smem8, stream, RG_ARGS(wa, wi), groups, (const float*)u_s);
     } else if (n >= 64 && (size_t)32 * Bs * sizeof(float) <= 48 * 1024) {
         xr_launch((k_rglru_gates<32>), dim3((n + 31) / 32, B, (Bs + RG_COLS - 1) / RG_COLS), dim3(RG_COLS), (size_t)32 * Bs * sizeof(float), stream, RG_ARGS(wa_t, wi_t));
     } else {
-        xr_launch((k_rglru_gates<8>), dim3((n + 7) / 8, B, (Bs + RG_COLS - 1) / RG_COLS), dim3(RG_COLS), (size_t)8 * Bs * sizeof(float), stream, RG_ARGS(wa_t, wi_t));
+        xr_launch((k_rglru_gates<8>), dim3((n + 7) / 8, B, (Bs + RG_COLS - 1) / RG_COLS), dim3(RG_COLS), smem8, stream, RG_ARGS(wa_t, wi_t));
     }
 #undef RG_ARGS
     dim3 gs((R + 127) / 128, n_seg);

@@ -130,14 +130,14 @@ def buzarax_config(size: str) -> BuzaraxConfig:
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
     moe = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": eff}}
     par = {"type": "parallel", "mixer": {
-        "left": {"heads": H, "kv_heads": K, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 50.0,
-                 "rot": {"base": 50000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "left": {"heads": H, "kv_heads": K, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0,
+                 "rot": {"base": 100000.0, "dims": rot, "scaling": {"factor": 16.0, "original": 8192, "fast": 16.0, "slow": 2.0}}},
         "right": {"heads": rh, "dim": rd, "vdim": rv, "decay": [1.0 - 2.0 ** -(3 + 5.0 * h / max(rh - 1, 1)) for h in range(rh)]},
-        "left_scale": 0.7, "right_scale": 1.1}}
+        "left_scale": 0.7, "right_scale": 0.9}}
     rec = {"type": "rglru", "mixer": {"width": R, "blocks": B, "conv": taps}}
     layers = [dict(par, mlp=dense), dict(rec, mlp=moe), dict(par, mlp=moe), dict(rec, mlp=dense), dict(par, mlp=dense), dict(rec, mlp=moe)]
     return BuzaraxConfig.from_dict({"architecture": "Buzarax", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
-                                    "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": layers})
+                                    "embedding": {"bigram": {"buckets": 65521, "mul_prev": 257, "mul_cur": 13}}, "layers": layers})
 
 
 def llama_like_buzarax(size: str, positions: int) -> LlamaConfig:
