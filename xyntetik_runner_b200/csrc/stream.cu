@@ -77,18 +77,21 @@ XR_EXPORT int xr_last_token(const int* ids, const int* feed, int n_feed, const i
 // With `clear`, d[t] is zeroed behind the read, ready for the next sublayer's products to add into.
 // `partial` (float32 [splits][n][width], or null): the sublayer's last products were cut along K and left their partial sums;
 // the row is then d[t] plus the partial sums in split order (plus `bias` [width], if any).
-// One block per row; the row is held in registers between the two passes (up to NA_OWN * 256 columns, more are read again);
+// One block per row; the row is held in registers between the two passes (columns beyond what the threads own are read again);
 // float32 throughout; the order of the sums depends on the width and the cut only.
 // ---------------------------------------------------------------------------
-#define NA_OWN 16
-template <typename T>
-__global__ void __launch_bounds__(256)
+// Two shapes: many rows, 256 threads a row with up to 16 columns each, one split's loads in flight at a time; few rows (a step of
+// single tokens, where the partial sums are many and nothing else hides their latency), 1,024 threads a row with up to 4 columns
+// each and eight splits' loads in flight together.  The sums are added in split order in both.
+template <typename T, int OWN, int BATCH>
+__global__ void __launch_bounds__(OWN <= 4 ? 1024 : 256)
 k_norm_add(float* __restrict__ d, float* __restrict__ x, const float* __restrict__ g, T* __restrict__ cast, int width, float eps, int clear,
            const float* __restrict__ partial, const float* __restrict__ bias, int splits, int n) {
     xr_pdl_launch();
     __shared__ float scratch[33];
     const float gain = g[0];
     xr_pdl_wait();
+    const int nt = blockDim.x;
     const size_t row = (size_t)blockIdx.x * width, split_stride = (size_t)n * width;
     float* dr = d + row;
     float* xr = x + row;
@@ -100,38 +103,42 @@ k_norm_add(float* __restrict__ d, float* __restrict__ x, const float* __restrict
         }
         return v;
     };
-    // a thread's columns of one split are independent loads, all in flight together; the splits are added in their order
-    float own[NA_OWN];
+    float own[OWN];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < NA_OWN; k++) {
-        const int i = threadIdx.x + k * 256;
+    for (int k = 0; k < OWN; k++) {
+        const int i = threadIdx.x + k * nt;
         own[k] = i < width ? dr[i] : 0.f;
     }
     if (partial != nullptr) {
-#pragma unroll 2
-        for (int s2 = 0; s2 < splits; s2++) {
-            const float* ps = partial + (size_t)s2 * split_stride + row;
-            float v[NA_OWN];
+        for (int s0 = 0; s0 < splits; s0 += BATCH) {
+            float v[BATCH][OWN];
 #pragma unroll
-            for (int k = 0; k < NA_OWN; k++) {
-                const int i = threadIdx.x + k * 256;
-                v[k] = i < width ? xr_ld_now(ps + i) : 0.f;
+            for (int b = 0; b < BATCH; b++) {
+                const float* ps = partial + (size_t)(s0 + b) * split_stride + row;
+#pragma unroll
+                for (int k = 0; k < OWN; k++) {
+                    const int i = threadIdx.x + k * nt;
+                    v[b][k] = (s0 + b < splits && i < width) ? xr_ld_now(ps + i) : 0.f;
+                }
             }
 #pragma unroll
-            for (int k = 0; k < NA_OWN; k++) { xr_ld_fence(v[k]); own[k] += v[k]; }
+            for (int b = 0; b < BATCH; b++) {
+#pragma unroll
+                for (int k = 0; k < OWN; k++) { xr_ld_fence(v[b][k]); own[k] += v[b][k]; }
+            }
         }
         if (bias != nullptr) {
 #pragma unroll
-            for (int k = 0; k < NA_OWN; k++) {
-                const int i = threadIdx.x + k * 256;
+            for (int k = 0; k < OWN; k++) {
+                const int i = threadIdx.x + k * nt;
                 if (i < width) own[k] += bias[i];
             }
         }
     }
 #pragma unroll
-    for (int k = 0; k < NA_OWN; k++) ss = fmaf(own[k], own[k], ss);
-    for (int i = threadIdx.x + NA_OWN * 256; i < width; i += 256) { const float v = value(i); ss = fmaf(v, v, ss); }
+    for (int k = 0; k < OWN; k++) ss = fmaf(own[k], own[k], ss);
+    for (int i = threadIdx.x + OWN * nt; i < width; i += nt) { const float v = value(i); ss = fmaf(v, v, ss); }
     ss = xr_block_sum(ss, scratch);
     const float inv = gain / sqrtf(ss / (float)width + eps);
     auto finish = [&](int i, float dv) {
@@ -141,21 +148,26 @@ k_norm_add(float* __restrict__ d, float* __restrict__ x, const float* __restrict
         if (clear) dr[i] = 0.f;
     };
 #pragma unroll
-    for (int k = 0; k < NA_OWN; k++) {
-        const int i = threadIdx.x + k * 256;
+    for (int k = 0; k < OWN; k++) {
+        const int i = threadIdx.x + k * nt;
         if (i < width) finish(i, own[k]);
     }
-    for (int i = threadIdx.x + NA_OWN * 256; i < width; i += 256) finish(i, value(i));
+    for (int i = threadIdx.x + OWN * nt; i < width; i += nt) finish(i, value(i));
 }
 
 XR_EXPORT int xr_norm_add(float* d, float* x, const float* g, void* cast, int cast_dtype, int n, int width, float eps, int clear,
                           const float* partial, const float* bias, int splits, cudaStream_t stream) {
     if (n < 1 || width < 1 || (partial != nullptr && splits < 1)) return XR_ERR_ARG;
-    if (cast == nullptr || cast_dtype == XR_F32)
-        xr_launch((k_norm_add<float>), dim3(n), dim3(256), 0, stream, d, x, g, (float*)cast, width, eps, clear, partial, bias, splits, n);
-    else if (cast_dtype == XR_BF16)
-        xr_launch((k_norm_add<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, d, x, g, (__nv_bfloat16*)cast, width, eps, clear, partial, bias, splits, n);
+    const bool few = n <= 32;
+#define NA(T)                                                                                                                                \
+    do {                                                                                                                                     \
+        if (few) xr_launch((k_norm_add<T, 4, 8>), dim3(n), dim3(1024), 0, stream, d, x, g, (T*)cast, width, eps, clear, partial, bias, splits, n); \
+        else xr_launch((k_norm_add<T, 16, 1>), dim3(n), dim3(256), 0, stream, d, x, g, (T*)cast, width, eps, clear, partial, bias, splits, n);   \
+    } while (0)
+    if (cast == nullptr || cast_dtype == XR_F32) NA(float);
+    else if (cast_dtype == XR_BF16) NA(__nv_bfloat16);
     else return XR_ERR_ARG;
+#undef NA
     return xr_launch_status();
 }
 
