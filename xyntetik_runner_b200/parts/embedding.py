@@ -10,7 +10,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorSpec
-from .base import Part
+from .base import Part, StateNeed
 from .linear import Linear
 
 
@@ -46,7 +46,6 @@ class PairEmbedding(Embedding):
         self.pairs = None
 
     def state_need(self):
-        from .base import StateNeed
         return StateNeed((1,), torch.int32)
 
     def tensors(self):
